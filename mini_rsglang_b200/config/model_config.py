@@ -460,3 +460,119 @@ class SatedraConfig(ModelConfig):
         if self.eos_token_id is not None:
             out["eos_token_id"] = self.eos_token_id
         return out
+
+
+@dataclass
+class NubipelConfig(ModelConfig):
+    """Nubipel: a decoder of layers whose two branches, a mixer and a dense feed-forward, read one RMS norm's output side by
+    side.  The mixer is an attention without rotation (query and key heads normed, sight in chunks of positions, a learned
+    sink a head in the softmax), a latent attention without rotation (queries through a latent of their own, keys and values
+    from one cached latent, every value element gated) or a gated delta rule (short convolutions, unit-length queries and
+    keys, a matrix state a head).  Embeddings are scaled, the output head reads the embedding table, and the logits are
+    scaled and bent by a tanh.  config.json names the design under `architecture`; its keys are read as they stand there:
+
+      vocab, width, norm.eps, embedding.scale, logit_scale, logit_softcap
+      layers[i].type = "attention":        mixer.{heads, kv_heads, dim, vdim, scale, mask.size}
+      layers[i].type = "latent_attention": mixer.{heads, dim, vdim, kv_rank, q_rank, scale}
+      layers[i].type = "delta":            mixer.{heads, kv_heads, dim, vdim, conv}
+      layers[i].mlp = null | {kind: "dense", ff}
+
+    `embedding.scale`, `logit_scale` (1), `logit_softcap` (none) and an attention's `mask` (every earlier key) may be left
+    out.  The design states no longest context and no end-of-sequence token; `max_position_embeddings` and `eos_token_id`
+    are read if a file has them."""
+
+    width: int = 0
+    norm_eps: float = 0.0
+    embedding_scale: float = 1.0
+    logit_scale: float = 1.0
+    logit_softcap: float = 0.0
+    layers: list = None
+
+    MODEL_TYPES: ClassVar[tuple[str, ...]] = ("nubipel",)
+    NO_CONTEXT_LIMIT: ClassVar[int] = 1 << 22
+    MIXER_KEYS: ClassVar[dict] = {
+        "attention": {"heads": int, "kv_heads": int, "dim": int, "vdim": int, "scale": float},
+        "latent_attention": {"heads": int, "dim": int, "vdim": int, "kv_rank": int, "q_rank": int, "scale": float},
+        "delta": {"heads": int, "kv_heads": int, "dim": int, "vdim": int, "conv": int},
+    }
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "NubipelConfig":
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise InvalidRequest("config.json: missing key `norm` (an object with `eps`)")
+        layers = raw.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise InvalidRequest("config.json: `layers` must be a list of layers")
+        read = []
+        for i, layer in enumerate(layers):
+            if not isinstance(layer, dict):
+                raise InvalidRequest(f"config.json: layers[{i}] must be an object")
+            kind = _require(layer, "type", str, f"mixer of layer {i}")
+            if kind not in cls.MIXER_KEYS:
+                raise InvalidRequest(f"config.json: layers[{i}].type {kind!r}; known: {sorted(cls.MIXER_KEYS)}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, dict):
+                raise InvalidRequest(f"config.json: layers[{i}].mixer must be an object")
+            sizes = {key: _require(mixer, key, want, f"layers[{i}].mixer") for key, want in cls.MIXER_KEYS[kind].items()}
+            if kind == "attention" and mixer.get("mask") is not None:
+                if not isinstance(mixer["mask"], dict):
+                    raise InvalidRequest(f"config.json: layers[{i}].mixer.mask must be an object")
+                sizes["mask"] = {"size": _require(mixer["mask"], "size", int, "chunk of positions")}
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise InvalidRequest(f"config.json: layers[{i}].mlp must be null or an object")
+                mlp = {"kind": _require(mlp, "kind", str, "feed-forward kind"), "ff": _require(mlp, "ff", int, "feed-forward width")}
+            read.append({"type": kind, "mixer": sizes, "mlp": mlp})
+        embedding = raw.get("embedding")
+        if embedding is not None and not isinstance(embedding, dict):
+            raise InvalidRequest("config.json: `embedding` must be an object")
+        cfg = cls(model_type="nubipel", architectures=["Nubipel"], vocab_size=_require(raw, "vocab", int, "vocabulary"),
+                  max_position_embeddings=int(raw.get("max_position_embeddings") or cls.NO_CONTEXT_LIMIT),
+                  eos_token_id=raw.get("eos_token_id"), width=_require(raw, "width", int, "model width"),
+                  norm_eps=_require(norm, "eps", float, "norm epsilon"),
+                  embedding_scale=_require(embedding, "scale", float, "embedding scale") if embedding and embedding.get("scale") is not None else 1.0,
+                  logit_scale=_require(raw, "logit_scale", float, "logit scale") if raw.get("logit_scale") is not None else 1.0,
+                  logit_softcap=_require(raw, "logit_softcap", float, "logit cap") if raw.get("logit_softcap") is not None else 0.0,
+                  layers=read)
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.width <= 0 or self.max_position_embeddings <= 0:
+            raise InvalidRequest("invalid Nubipel dimensions: every size must be a positive integer")
+        if not math.isfinite(self.norm_eps) or self.norm_eps <= 0:
+            raise InvalidRequest("invalid normalization parameters")
+        if not all(math.isfinite(v) for v in (self.embedding_scale, self.logit_scale, self.logit_softcap)) or self.logit_softcap < 0:
+            raise InvalidRequest("embedding scale, logit scale and logit cap must be finite, the cap not negative")
+        for i, layer in enumerate(self.layers):
+            m = layer["mixer"]
+            for key, want in self.MIXER_KEYS[layer["type"]].items():
+                if m[key] <= 0 or not math.isfinite(m[key]):
+                    raise InvalidRequest(f"layers[{i}].mixer.{key} must be positive")
+            if "kv_heads" in m and m["heads"] % m["kv_heads"]:
+                raise InvalidRequest(f"layers[{i}]: heads must be a multiple of kv_heads")
+            if "mask" in m and m["mask"]["size"] <= 0:
+                raise InvalidRequest(f"layers[{i}].mixer.mask.size must be positive")
+            mlp = layer["mlp"]
+            if mlp is not None and (mlp["kind"] != "dense" or mlp["ff"] <= 0):
+                raise InvalidRequest(f"layers[{i}].mlp: only kind `dense` with a positive `ff` is built")
+        if self.eos_token_id is not None:
+            self.eos_ids()
+
+    def eos_ids(self, folder: str | None = None) -> list[int]:
+        if self.eos_token_id is None and (folder is None or not os.path.exists(os.path.join(folder, "generation_config.json"))):
+            return []                # the design names no end-of-sequence token: generation ends by length
+        return super().eos_ids(folder)
+
+    def to_dict(self) -> dict:
+        out = {"architecture": "Nubipel", "vocab": self.vocab_size, "width": self.width, "norm": {"eps": self.norm_eps},
+               "embedding": {"scale": self.embedding_scale}, "logit_scale": self.logit_scale, "layers": self.layers}
+        if self.logit_softcap:
+            out["logit_softcap"] = self.logit_softcap
+        if self.max_position_embeddings != self.NO_CONTEXT_LIMIT:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_id is not None:
+            out["eos_token_id"] = self.eos_token_id
+        return out

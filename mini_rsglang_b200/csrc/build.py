@@ -184,7 +184,10 @@ def kernel_library() -> ctypes.CDLL:
 
 
 HYBRID_KERNEL_SOURCES = ("hybrid_elementwise.cu", "ssm_scan.cu")
-LATENT_KERNEL_SOURCES = ("latent_elementwise.cu", "experts.cu", "experts_mma.cu")
+LATENT_KERNEL_SOURCES = ("latent_elementwise.cu",)
+EXPERT_KERNEL_SOURCES = ("experts.cu", "experts_mma.cu")
+PARALLEL_KERNEL_SOURCES = ("parallel_elementwise.cu",)
+DELTA_KERNEL_SOURCES = ("delta_rule.cu",)
 
 
 def _kernel_group(key: str, name: str, sources: tuple[str, ...]) -> ctypes.CDLL:
@@ -204,9 +207,25 @@ def hybrid_kernel_library() -> ctypes.CDLL:
 
 
 def latent_kernel_library() -> ctypes.CDLL:
-    """The kernels of layer norms with bias, latent attention and routed experts (every size at run time); compiled
-    when a model first needs one of them."""
+    """The kernels of layer norms with bias and latent attention (every size at run time); compiled when a model first
+    needs one of them."""
     return _kernel_group("latent", "mrs_latent", LATENT_KERNEL_SOURCES)
+
+
+def expert_kernel_library() -> ctypes.CDLL:
+    """The kernels of routed experts (every size at run time); compiled when a model first needs one of them."""
+    return _kernel_group("experts", "mrs_experts", EXPERT_KERNEL_SOURCES)
+
+
+def parallel_kernel_library() -> ctypes.CDLL:
+    """The kernels of layers whose branches run side by side, of plain feed-forwards and of capped logits (every size
+    at run time); compiled when a model first needs one of them."""
+    return _kernel_group("parallel", "mrs_parallel", PARALLEL_KERNEL_SOURCES)
+
+
+def delta_kernel_library() -> ctypes.CDLL:
+    """The kernels of the gated delta rule (every size at run time); compiled when a model first needs them."""
+    return _kernel_group("delta", "mrs_delta", DELTA_KERNEL_SOURCES)
 
 
 def biased_attention_library() -> ctypes.CDLL:
@@ -238,7 +257,8 @@ SPECIALISED_BUILDS = tuple((lambda d=d: specialised_kernel_library("attention_mm
     tuple((lambda d=d: specialised_kernel_library("attention_decode_tma.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128)) + \
     tuple((lambda d=d: specialised_kernel_library("attention_prefill_tc.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128)) + \
     (lambda: specialised_kernel_library("gemm_tc.cu", {}), lambda: specialised_kernel_library("gemm_many_rows.cu", {}),
-     hybrid_kernel_library, latent_kernel_library, biased_attention_library,
+     hybrid_kernel_library, latent_kernel_library, expert_kernel_library, parallel_kernel_library, delta_kernel_library,
+     biased_attention_library,
      lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 128, "MRS_VALUE_DIM": 128}),
      lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 64, "MRS_VALUE_DIM": 32}),
      lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 288, "MRS_VALUE_DIM": 256, "MRS_VALUES_IN_KEYS": 1}),

@@ -2,7 +2,9 @@
 //   score = (q . k) * scale;  score <- cap * tanh(score / cap)  (cap > 0);
 //   score += bias[min(i - j, bias_rows - 1), head]              (a table by distance, float32);
 //   key j is seen by query i when j <= i and (i - j < window or j < keep_first)   (window 0: every key);
-//   softmax with a sink: p_j = exp(s_j) / (1 + sum exp(s_j))    (sink != 0), else the usual one;
+//   or, with chunk > 0 (and no window), when j <= i and floor(j / chunk) = floor(i / chunk): chunks counted from position 0;
+//   softmax with a sink: p_j = exp(s_j) / (exp(z) + sum exp(s_j))   (sink != 0; z = sink_logits[head], or 0 without a table:
+//   one more term in the denominator that has no key and no value and is not scaled), else the usual one;
 //   out = (sum p_j v_j) * gate[token, head]                     (gate float32, may be null).
 // Keys have d elements a head and values e (the two need not agree).  Scores, softmax and sums are float32.
 // Without value pages the values are the first e elements of the key rows (a latent that serves as key and as
@@ -25,7 +27,7 @@ __global__ void attention_biased_simt_kernel(const T* __restrict__ q, const T* _
                                              const int* __restrict__ block_table, const float* __restrict__ bias,
                                              const float* __restrict__ gate, T* __restrict__ out, int tokens, int nq, int nkv,
                                              int d, int e, int page_size, int table_width, float scale, float cap, int window,
-                                             int keep_first, int bias_rows, int sink) {
+                                             int keep_first, int bias_rows, int sink, const float* __restrict__ sink_logits, int chunk) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float q_s[ATTN_WARPS][ATTN_MAX_D];
@@ -36,8 +38,9 @@ __global__ void attention_biased_simt_kernel(const T* __restrict__ q, const T* _
     const int g = h / (nq / nkv);
     const int pos = positions[t];
     const int length = pos + 1;
-    const int first = window > 0 ? max(0, length - window) : 0;     // first position of the window
-    const int kept = min(keep_first, first);                        // positions [0, kept) lie before it and stay seen
+    // first position of the window, or of the query's chunk
+    const int first = chunk > 0 ? (pos / chunk) * chunk : (window > 0 ? max(0, length - window) : 0);
+    const int kept = chunk > 0 ? 0 : min(keep_first, first);        // positions [0, kept) lie before a window and stay seen
     const int seen = kept + (length - first);
     const int* pages = block_table + (size_t)seq_of_token[t] * table_width;
     const T* q_row = q + ((size_t)t * nq + h) * d;
@@ -49,7 +52,7 @@ __global__ void attention_biased_simt_kernel(const T* __restrict__ q, const T* _
     float acc[EREGS];
 #pragma unroll
     for (int i = 0; i < EREGS; ++i) acc[i] = 0.0f;
-    float running_max = sink ? 0.0f : -CUDART_INF_F, running_sum = sink ? 1.0f : 0.0f;
+    float running_max = sink ? (sink_logits ? sink_logits[h] : 0.0f) : -CUDART_INF_F, running_sum = sink ? 1.0f : 0.0f;
 
     for (int base = 0; base < seen; base += 32) {
         const int u = base + lane;
@@ -98,17 +101,18 @@ __global__ void attention_biased_simt_kernel(const T* __restrict__ q, const T* _
 MRS_EXPORT int mrs_attention_biased_simt(int is_bf16, const void* q, const void* k_cache, const void* v_cache, const int* positions,
                                          const int* seq_of_token, const int* block_table, const float* bias, const float* gate,
                                          void* out, int tokens, int nq, int nkv, int d, int e, int page_size, int table_width,
-                                         float scale, float cap, int window, int keep_first, int bias_rows, int sink, void* stream) {
+                                         float scale, float cap, int window, int keep_first, int bias_rows, int sink,
+                                         const float* sink_logits, int chunk, void* stream) {
     if (tokens <= 0) return 0;
     if (d <= 0 || d > ATTN_MAX_D || e <= 0 || e > ATTN_MAX_E || (!v_cache && e > d) || nkv <= 0 || nq % nkv || (bias && bias_rows <= 0) || window < 0 ||
-        keep_first < 0)
+        keep_first < 0 || chunk < 0 || (chunk > 0 && window > 0) || (sink_logits && !sink))
         return MRS_BAD_ARGUMENT;
     const long long units = (long long)tokens * nq;
     const unsigned blocks = (unsigned)((units + ATTN_WARPS - 1) / ATTN_WARPS);
 #define MRS_BIASED_SIMT(T, EREGS)                                                                                              \
     MRS_LAUNCH((attention_biased_simt_kernel<T, EREGS>), blocks, 32 * ATTN_WARPS, 0, stream, (const T*)q, (const T*)k_cache,      \
                (const T*)v_cache, positions, seq_of_token, block_table, bias, gate, (T*)out, tokens, nq, nkv, d, e, page_size,    \
-               table_width, scale, cap, window, keep_first, bias_rows, sink)
+               table_width, scale, cap, window, keep_first, bias_rows, sink, sink_logits, chunk)
     if (is_bf16) {
         if (e <= 128) MRS_BIASED_SIMT(bf16, 4); else if (e <= 256) MRS_BIASED_SIMT(bf16, 8); else if (e <= 512) MRS_BIASED_SIMT(bf16, 16); else MRS_BIASED_SIMT(bf16, 32);
     } else {

@@ -76,7 +76,12 @@ struct Extras {            // what is put around the scores
     int bias_rows;
     float scale, cap;      // cap 0: none
     int window, keep_first, sink;
+    const float* sink_logits;   // [nq]: the sink's term is exp(sink_logits[head]); null: exp(0)
+    int chunk;                  // > 0 (and no window): a query sees the keys of its own chunk of positions only
 };
+
+// The sink's logit of a query head, in units of log 2.
+__device__ __forceinline__ float sink_of(const Extras& x, int head) { return x.sink_logits ? x.sink_logits[head] * LOG2E : 0.0f; }
 
 // Keys [key0, key0 + KV) of one kv head into a [KV][W] shared tile; rows at or beyond `key_end` or on a page that was
 // given back are zeros.
@@ -152,8 +157,8 @@ __device__ __forceinline__ void pv_product(float (&o)[E / 8][4], const float (&s
 // sum of its two rows (lane / 4 and lane / 4 + 8), rescales the accumulator and turns the scores into weights.
 template <int NT>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[E / 8][4], float (&row_max)[2], float (&row_sum)[2],
-                                             const int (&row_pos)[2], const int (&row_head)[2], int key0, int key_end, int nq,
-                                             const Extras& x) {
+                                             const int (&row_pos)[2], const int (&row_head)[2], const int (&row_lo)[2], int key0,
+                                             int key_end, int nq, const Extras& x) {
     const int t = threadIdx.x & 3;
     float block_max[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
@@ -163,7 +168,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[E / 8
             const int key = key0 + nt * 8 + 2 * t + (e & 1);
             const int pos = row_pos[e >> 1];
             const int back = pos - key;
-            const bool seen = back >= 0 && key < key_end && (x.window <= 0 || back < x.window || key < x.keep_first);
+            const bool seen = back >= 0 && key < key_end && key >= row_lo[e >> 1] && (x.window <= 0 || back < x.window || key < x.keep_first);
             float v = -CUDART_INF_F;
             if (seen) {
                 v = s[nt][e] * x.scale;
@@ -205,7 +210,7 @@ struct Blocks {
 };
 __device__ __forceinline__ Blocks blocks_of(int first_pos, int key_end, int kv, const Extras& x) {
     Blocks b;
-    const int key_begin = x.window > 0 ? max(0, first_pos - x.window + 1) : 0;
+    const int key_begin = x.chunk > 0 ? (first_pos / x.chunk) * x.chunk : (x.window > 0 ? max(0, first_pos - x.window + 1) : 0);
     b.window_first = key_begin / kv;
     const int kept_keys = x.window > 0 ? min(x.keep_first, key_begin) : 0;
     b.kept = min((kept_keys + kv - 1) / kv, b.window_first);
@@ -239,12 +244,13 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
     const int key_end = last_pos + 1;
     const Blocks blocks = blocks_of(first_pos, key_end, KV_WIDE, x);
 
-    int row_pos[2], row_head[2];
+    int row_pos[2], row_head[2], row_lo[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = warp * 16 + (lane >> 2) + 8 * r;
         row_pos[r] = row < rows ? positions[tile.first_token + row / group] : last_pos;
         row_head[r] = kv_head * group + row % group;
+        row_lo[r] = x.chunk > 0 ? (row_pos[r] / x.chunk) * x.chunk : 0;
     }
     float o[E / 8][4];
 #pragma unroll
@@ -254,7 +260,7 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
     float row_max[2], row_sum[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        row_max[r] = x.sink ? 0.0f : -CUDART_INF_F;
+        row_max[r] = x.sink ? sink_of(x, row_head[r]) : -CUDART_INF_F;
         row_sum[r] = x.sink && (lane & 3) == 0 ? 1.0f : 0.0f;
     }
 
@@ -283,7 +289,7 @@ __global__ void __launch_bounds__(THREADS) attention_biased_rows_kernel(
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
             qk_product<NT>(s, q_tile, warp * 16, k_tiles + stage * KV_WIDE * LD<D>, 0);
-            softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, key0, key_end, nq, x);
+            softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, row_lo, key0, key_end, nq, x);
             pv_product<NT>(o, s, v_tiles + stage * KV_WIDE * LD<VW>, 0);
         }
         __syncthreads();
@@ -333,12 +339,13 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
     const int split = blockIdx.z, share = (blocks.count + splits - 1) / splits;
     const int block_first = min(blocks.count, split * share), block_last = min(blocks.count, block_first + share);
 
-    int row_pos[2], row_head[2];
+    int row_pos[2], row_head[2], row_lo[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + 8 * r;
         row_pos[r] = row < rows ? positions[tile.first_token + row / group] : last_pos;
         row_head[r] = kv_head * group + row % group;
+        row_lo[r] = x.chunk > 0 ? (row_pos[r] / x.chunk) * x.chunk : 0;
     }
     float o[E / 8][4];
 #pragma unroll
@@ -371,7 +378,7 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
             qk_product<NT>(s, q_tile, 0, k_tiles + stage * KV_NARROW * LD<D>, warp * 16);
-            softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, key0, key_end, nq, x);
+            softmax_step<NT>(s, o, row_max, row_sum, row_pos, row_head, row_lo, key0, key_end, nq, x);
             pv_product<NT>(o, s, v_tiles + stage * KV_NARROW * LD<VW>, warp * 16);
         }
         __syncthreads();
@@ -404,11 +411,12 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
         const int row = idx / E, col = idx % E;
         if (row >= rows) continue;
         const bool with_sink = x.sink && splits == 1;          // among several CTAs the sink joins in the combine kernel
-        float m = with_sink ? 0.0f : -CUDART_INF_F;
+        const float sink_logit = with_sink ? sink_of(x, kv_head * group + row % group) : 0.0f;
+        float m = with_sink ? sink_logit : -CUDART_INF_F;
 #pragma unroll
         for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * ROWS_NARROW + row) * 2]);
         const float base = m == -CUDART_INF_F ? 0.0f : m;
-        float sum = with_sink ? exp2f(-base) : 0.0f, acc = 0.0f;
+        float sum = with_sink ? exp2f(sink_logit - base) : 0.0f, acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float f = exp2f(merge_ml[(w * ROWS_NARROW + row) * 2] - base);
@@ -430,7 +438,7 @@ __global__ void __launch_bounds__(THREADS) attention_biased_keys_kernel(
 // Merges the partial results of a tile's `splits` CTAs, adds the sink and applies the gate.
 __global__ void __launch_bounds__(THREADS) attention_biased_combine_kernel(
     const float* __restrict__ part_o, const float* __restrict__ part_ml, const Tile* __restrict__ tiles, bf16* __restrict__ out,
-    const float* __restrict__ gate, int nq, int nkv, int splits, int sink) {
+    const float* __restrict__ gate, int nq, int nkv, int splits, int sink, const float* __restrict__ sink_logits) {
     pdl_launch_dependents();
     pdl_wait();
     const Tile tile = tiles[blockIdx.x];
@@ -438,11 +446,12 @@ __global__ void __launch_bounds__(THREADS) attention_biased_combine_kernel(
     const size_t base_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS_NARROW;
     const int row = blockIdx.z;                       // a CTA a row: few tiles still fill the GPU
     if (row >= rows) return;
+    const float sink_logit = sink && sink_logits ? sink_logits[kv_head * group + row % group] * LOG2E : 0.0f;
     for (int col = threadIdx.x; col < E; col += THREADS) {
-        float m = sink ? 0.0f : -CUDART_INF_F;
+        float m = sink ? sink_logit : -CUDART_INF_F;
         for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base_slot + (size_t)s * ROWS_NARROW + row) * 2]);
         const float base = m == -CUDART_INF_F ? 0.0f : m;
-        float sum = sink ? exp2f(-base) : 0.0f, acc = 0.0f;
+        float sum = sink ? exp2f(sink_logit - base) : 0.0f, acc = 0.0f;
         for (int s = 0; s < splits; ++s) {
             const size_t slot = base_slot + (size_t)s * ROWS_NARROW + row;
             const float f = exp2f(part_ml[slot * 2] - base);
@@ -483,16 +492,16 @@ MRS_EXPORT int mrs_attention_biased_mma(int narrow, const void* q, const void* k
                                         const int* block_table, int table_width, const int* tiles, int num_tiles, void* out,
                                         const float* bias, int bias_rows, const float* gate, int nq, int nkv, int page_size,
                                         float scale, float cap, int window, int keep_first, int sink, int splits, float* scratch,
-                                        void* stream) {
+                                        const float* sink_logits, int chunk, void* stream) {
     if (num_tiles <= 0) return 0;
     if (splits < 1 || splits > 65535 || (splits > 1 && (!narrow || !scratch)) || (!IN_KEYS && !v_cache)) return MRS_BAD_ARGUMENT;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || nkv <= 0 || nq % nkv || nq / nkv > (narrow ? ROWS_NARROW : ROWS_WIDE) || (bias && bias_rows <= 0) || window < 0 ||
-        keep_first < 0)
+        keep_first < 0 || chunk < 0 || (chunk > 0 && window > 0) || (sink_logits && !sink))
         return MRS_BAD_ARGUMENT;
     Extras x;
     x.bias = bias, x.gate = gate, x.bias_rows = bias_rows, x.scale = scale, x.cap = cap, x.window = window, x.keep_first = keep_first;
-    x.sink = sink;
+    x.sink = sink, x.sink_logits = sink_logits, x.chunk = chunk;
     static bool configured[2] = {false, false};
     if (!configured[narrow ? 1 : 0]) {
         cudaError_t e = narrow
@@ -509,7 +518,7 @@ MRS_EXPORT int mrs_attention_biased_mma(int narrow, const void* q, const void* k
                    page_size, shift, x, part_o, part_ml, splits);
         if (splits > 1)
             MRS_LAUNCH(attention_biased_combine_kernel, dim3(num_tiles, nkv, ROWS_NARROW), E < THREADS ? 32 * ((E + 31) / 32) : THREADS, 0, stream, (const float*)part_o,
-                       (const float*)part_ml, (const Tile*)tiles, (bf16*)out, gate, nq, nkv, splits, sink);
+                       (const float*)part_ml, (const Tile*)tiles, (bf16*)out, gate, nq, nkv, splits, sink, sink_logits);
     } else
         MRS_LAUNCH(attention_biased_rows_kernel, dim3(num_tiles, nkv), THREADS, smem_rows, stream, (const bf16*)q, (const bf16*)k_cache,
                    (const bf16*)v_cache, positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, nq, nkv, page_size, shift, x);

@@ -26,29 +26,29 @@ MRS_EXPORT int mrs_patch_tokens(int* ids, const int* rows, const int* index, con
 }
 
 // ---------------------------------------------------------------------------------------------
-// Embedding: residual[t, :] = float(table[ids[t], :])      (reference: ops.cu:15-18)
+// Embedding: residual[t, :] = float(table[ids[t], :]) * scale   (reference: ops.cu:15-18; a design may scale its embeddings)
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ residual, int width) {
+                             float* __restrict__ residual, int width, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const T* row = table + (size_t)ids[t] * width;
     float* out = residual + (size_t)t * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = to_float(row[i]) * scale;
 }
 
 MRS_EXPORT int mrs_embed(int is_bf16, const void* table, const int* ids, float* residual,
-                         int tokens, int width, void* stream) {
+                         int tokens, int width, float scale, void* stream) {
     if (tokens <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (is_bf16)
         MRS_LAUNCH(embed_kernel<bf16>, tokens, threads, 0, stream,
-            (const bf16*)table, ids, residual, width);
+            (const bf16*)table, ids, residual, width, scale);
     else
         MRS_LAUNCH(embed_kernel<float>, tokens, threads, 0, stream,
-            (const float*)table, ids, residual, width);
+            (const float*)table, ids, residual, width, scale);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

@@ -205,12 +205,69 @@ __global__ void qkv_bias_store_kernel(const float* __restrict__ proj, const floa
     }
 }
 
+// The same with an RMS norm over every query and key head before it leaves (weights q_norm, k_norm [d] float32, shared by
+// the heads; x / sqrt(mean(x^2) + eps) * w after the bias): one warp a head, so that a head's sum of squares is a few
+// shuffles.  No blending of values.
+template <typename T>
+__global__ void qkv_headnorm_store_kernel(const float* __restrict__ proj, const float* __restrict__ bias, const float* __restrict__ q_norm,
+                                          const float* __restrict__ k_norm, float eps, T* __restrict__ q_out, T* __restrict__ k_cache,
+                                          T* __restrict__ v_cache, const int* __restrict__ slots, float* __restrict__ gate_out, int nq,
+                                          int nkv, int d, int e, int page_size, int has_gate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int qw = nq * d, kw = nkv * d, vw = nkv * e;
+    const int total = qw + kw + vw + (has_gate ? nq : 0);
+    const float* row = proj + t * total;
+    const int slot = slots ? slots[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, in_page = slot >= 0 ? slot % page_size : 0;
+    for (int unit = warp; unit < nq + 2 * nkv; unit += warps) {
+        if (unit < nq + nkv) {                               // a query or key head
+            const bool is_q = unit < nq;
+            const int head = is_q ? unit : unit - nq, at = is_q ? head * d : qw + head * d;
+            const float* w = is_q ? q_norm : k_norm;
+            if (!is_q && (slot < 0 || !k_cache)) continue;
+            float sum = 0.0f;
+            for (int x = lane; x < d; x += 32) {
+                const float v = row[at + x] + (bias ? bias[at + x] : 0.0f);
+                sum += v * v;
+            }
+            const float scale = w ? 1.0f / sqrtf(warp_sum(sum) / (float)d + eps) : 1.0f;
+            T* dst = is_q ? q_out + t * qw + (size_t)head * d : k_cache + (((size_t)page * nkv + head) * page_size + in_page) * d;
+            for (int x = lane; x < d; x += 32) {
+                const float v = row[at + x] + (bias ? bias[at + x] : 0.0f);
+                dst[x] = from_float<T>(w ? v * scale * w[x] : v);
+            }
+        } else if (slot >= 0 && v_cache) {                   // a value head
+            const int head = unit - nq - nkv, at = qw + kw + head * e;
+            T* dst = v_cache + (((size_t)page * nkv + head) * page_size + in_page) * e;
+            for (int x = lane; x < e; x += 32) dst[x] = from_float<T>(row[at + x] + (bias ? bias[at + x] : 0.0f));
+        }
+    }
+    if (has_gate)
+        for (int h = threadIdx.x; h < nq; h += blockDim.x) gate_out[t * nq + h] = 1.0f / (1.0f + expf(-row[qw + kw + vw + h]));
+}
+
 MRS_EXPORT int mrs_qkv_bias_store(int is_bf16, const float* proj, const float* bias, void* q_out, void* k_cache, void* v_cache,
                                   const int* slots, float* v_first, float* gate_out, int tokens, int nq, int nkv, int d, int e,
-                                  int page_size, int mix_mode, float lambda, int has_gate, void* s) {
+                                  int page_size, int mix_mode, float lambda, int has_gate, const float* q_norm, const float* k_norm,
+                                  float norm_eps, void* s) {
     if (tokens <= 0) return 0;
-    if (nq <= 0 || nkv <= 0 || d <= 0 || e <= 0 || page_size <= 0 || (mix_mode && !v_first) || (has_gate && !gate_out))
+    if (nq <= 0 || nkv <= 0 || d <= 0 || e <= 0 || page_size <= 0 || (mix_mode && !v_first) || (has_gate && !gate_out) ||
+        ((q_norm || k_norm) && mix_mode))
         return MRS_BAD_ARGUMENT;
+    if (q_norm || k_norm) {
+        const int units = nq + 2 * nkv;
+        const int threads = units >= 8 ? 256 : (units >= 4 ? 128 : 64);
+        if (is_bf16)
+            MRS_LAUNCH(qkv_headnorm_store_kernel<bf16>, tokens, threads, 0, s, proj, bias, q_norm, k_norm, norm_eps, (bf16*)q_out,
+                       (bf16*)k_cache, (bf16*)v_cache, slots, gate_out, nq, nkv, d, e, page_size, has_gate);
+        else
+            MRS_LAUNCH(qkv_headnorm_store_kernel<float>, tokens, threads, 0, s, proj, bias, q_norm, k_norm, norm_eps, (float*)q_out,
+                       (float*)k_cache, (float*)v_cache, slots, gate_out, nq, nkv, d, e, page_size, has_gate);
+        MRS_RETURN_LAUNCH_STATUS();
+    }
     if (is_bf16)
         MRS_LAUNCH(qkv_bias_store_kernel<bf16>, tokens, 256, 0, s, proj, bias, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, slots,
                    v_first, gate_out, nq, nkv, d, e, page_size, mix_mode, lambda, has_gate);

@@ -8,6 +8,11 @@
 //                     the rotated query parts behind the latent columns of the query rows, the latent divided by its
 //                     root mean square and the rotated key part into the cache row of the token, sigmoid of the gates
 //
+//   latent_norms      for a latent attention whose queries pass a latent of their own and that rotates nothing: after the
+//                     fused projection query latent | key/value latent | ..., both divided by their root mean squares times
+//                     their weights; the first goes on to the queries' up-projection, the second into the cache row
+//   sigmoid_gate_mul  x <- x * sigmoid(gate) element by element, the gate a column range of wider float32 rows
+//
 // Rotation: of the first `rotary` elements of a rotated part element i pairs with i + rotary / 2; the pair (u, v) at
 // position p becomes (u c - v s, v c + u s) with c = m cos(p f_i), s = m sin(p f_i); the rest passes unchanged.
 #include "common.cuh"
@@ -188,6 +193,42 @@ __global__ void latent_prepare_kernel(const float* __restrict__ proj, int proj_w
         for (int h = threadIdx.x; h < z.heads; h += blockDim.x) gate[(size_t)t * z.heads + h] = 1.0f / (1.0f + expf(-row[at + h]));
 }
 
+// One block a token.  Columns of a projected row: q_rank of the query latent, then `latent` of the key/value latent.
+template <typename T>
+__global__ void latent_norms_kernel(const float* __restrict__ proj, int proj_width, const float* __restrict__ q_weight,
+                                    const float* __restrict__ latent_weight, float eps, const int* __restrict__ slots,
+                                    T* __restrict__ q_latent, T* __restrict__ cache, int q_rank, int latent) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const size_t t = blockIdx.x;
+    const float* row = proj + t * proj_width;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) sum += row[i] * row[i];
+    const float q_scale = rsqrtf(block_sum(sum, scratch) / (float)q_rank + eps);
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) q_latent[t * q_rank + i] = from_float<T>(row[i] * q_scale * q_weight[i]);
+    const int slot = slots ? slots[t] : -1;
+    if (slot < 0 || !cache) return;
+    const float* low = row + q_rank;
+    sum = 0.0f;
+    for (int i = threadIdx.x; i < latent; i += blockDim.x) sum += low[i] * low[i];
+    const float scale = rsqrtf(block_sum(sum, scratch) / (float)latent + eps);
+    T* dst = cache + (size_t)slot * latent;
+    for (int i = threadIdx.x; i < latent; i += blockDim.x) dst[i] = from_float<T>(low[i] * scale * latent_weight[i]);
+}
+
+template <typename T>
+__global__ void sigmoid_gate_mul_kernel(T* __restrict__ x, const float* __restrict__ gate, int gate_stride, int tokens, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    for (int t = blockIdx.y; t < tokens; t += gridDim.y) {
+        const float g = gate[(size_t)t * gate_stride + c];
+        x[(size_t)t * width + c] = from_float<T>(to_float(x[(size_t)t * width + c]) / (1.0f + expf(-g)));
+    }
+}
+
 }  // namespace
 
 MRS_EXPORT int mrs_add_layernorm(int is_bf16, float* residual, const void* delta, const float* weight, const float* bias, float eps,
@@ -245,5 +286,35 @@ MRS_EXPORT int mrs_latent_prepare(int is_bf16, const float* proj, int proj_width
     else
         MRS_LAUNCH(latent_prepare_kernel<float>, tokens, 256, smem, stream, proj, proj_width, latent_weight, eps, inv_freq, magnitude,
                    positions, slots, (float*)q_plain, (float*)q_rows, (float*)cache, gate, tokens, z);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// q_latent [tokens, q_rank]; cache rows of `latent` elements addressed by `slots` (null or a slot of -1: nothing is kept).
+MRS_EXPORT int mrs_latent_norms(int is_bf16, const float* proj, int proj_width, const float* q_weight, const float* latent_weight,
+                                float eps, const int* slots, void* q_latent, void* cache, int tokens, int q_rank, int latent,
+                                void* stream) {
+    if (tokens <= 0) return 0;
+    if (q_rank <= 0 || latent <= 0 || proj_width < q_rank + latent || !q_weight || !latent_weight) return MRS_BAD_ARGUMENT;
+    if (is_bf16)
+        MRS_LAUNCH(latent_norms_kernel<bf16>, tokens, 128, 0, stream, proj, proj_width, q_weight, latent_weight, eps, slots,
+                   (bf16*)q_latent, (bf16*)cache, q_rank, latent);
+    else
+        MRS_LAUNCH(latent_norms_kernel<float>, tokens, 128, 0, stream, proj, proj_width, q_weight, latent_weight, eps, slots,
+                   (float*)q_latent, (float*)cache, q_rank, latent);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// x [tokens, width] of the engine's dtype, in place; gate: float32 rows of gate_stride elements, the columns at `gate`.
+MRS_EXPORT int mrs_sigmoid_gate_mul(int is_bf16, void* x, const float* gate, int gate_stride, int tokens, int width, void* stream) {
+    if (tokens <= 0 || width <= 0) return 0;
+    const int threads = 128;
+    const unsigned across = (unsigned)((width + threads - 1) / threads);
+    long long down = ((long long)mrs_sm_count() * 16 + across - 1) / across;
+    if (down > tokens) down = tokens;
+    if (down > 65535) down = 65535;
+    if (is_bf16)
+        MRS_LAUNCH(sigmoid_gate_mul_kernel<bf16>, dim3(across, (unsigned)down), threads, 0, stream, (bf16*)x, gate, gate_stride, tokens, width);
+    else
+        MRS_LAUNCH(sigmoid_gate_mul_kernel<float>, dim3(across, (unsigned)down), threads, 0, stream, (float*)x, gate, gate_stride, tokens, width);
     MRS_RETURN_LAUNCH_STATUS();
 }

@@ -18,7 +18,7 @@ from .errors import BackendError, InvalidRequest
 _c_int, _c_vp, _c_float = ctypes.c_int, ctypes.c_void_p, ctypes.c_float
 
 _SIGNATURES = {
-    "mrs_embed": [_c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_embed": [_c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_float, _c_vp],
     "mrs_patch_tokens": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp],
     "mrs_add_rmsnorm": [_c_int, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_rmsnorm": [_c_int, _c_vp, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_vp],
@@ -119,8 +119,8 @@ def _is_bf16(dtype: torch.dtype) -> int:
     raise InvalidRequest(f"activations must be bfloat16 or float32, got {dtype}")
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) -> None:
-    """residual[t, :] = float32(table[ids[t], :])."""
+def embed(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor, scale: float = 1.0) -> None:
+    """residual[t, :] = float32(table[ids[t], :]) * scale."""
     tokens, width = residual.shape
     _need(table, None, "embed table")
     _need(ids, torch.int32, "embed ids", (tokens,))
@@ -128,7 +128,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) -> Non
     if table.shape[1] != width:
         raise InvalidRequest("embed: width mismatch")
     _check(library().mrs_embed(_is_bf16(table.dtype), table.data_ptr(), ids.data_ptr(), residual.data_ptr(),
-                               tokens, width, _stream()), "embed")
+                               tokens, width, float(scale), _stream()), "embed")
 
 
 def patch_tokens(ids: torch.Tensor, rows: torch.Tensor, index: torch.Tensor, sampled: torch.Tensor, vocab: int) -> None:
@@ -1021,7 +1021,7 @@ _HYBRID_SIGNATURES = {
     "mrs_postnorm_add_norm": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_float, _c_vp, _c_int, _c_int, _c_vp],
     "mrs_glu_clamped": [_c_int, _c_vp, _c_vp, _c_int, _c_int, _c_float, _c_float, _c_vp],
     "mrs_qkv_bias_store": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int,
-                           _c_int, _c_int, _c_float, _c_int, _c_vp],
+                           _c_int, _c_int, _c_float, _c_int, _c_vp, _c_vp, _c_float, _c_vp],
     "mrs_gated_part_norm": [_c_int, _c_vp, _c_vp, _c_int, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_causal_conv_silu": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_ll, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int,
                              _c_int, _c_int, _c_int, _c_vp],
@@ -1076,11 +1076,13 @@ def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: f
 def qkv_bias_store(proj: torch.Tensor, bias: torch.Tensor | None, q_out: torch.Tensor, k_cache: torch.Tensor | None,
                    v_cache: torch.Tensor | None, slots: torch.Tensor | None, nq: int, nkv: int, d: int, e: int,
                    v_first: torch.Tensor | None = None, mix_mode: int = 0, mix: float = 0.0,
-                   gate_out: torch.Tensor | None = None) -> None:
+                   gate_out: torch.Tensor | None = None, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
+                   norm_eps: float = 0.0) -> None:
     """After the fused projection q | k | v (| one gate column a query head), float32: biases added, q to `q_out`, k into
     the key pages [pages, nkv, page, d], v into the value pages [pages, nkv, page, e] at `slots`, sigmoid(gate) to
     `gate_out` [tokens, nq] float32.  `mix_mode` 1 leaves this layer's values in `v_first` [tokens, nkv * e] float32;
-    2 stores (1 - mix) v + mix v_first instead of v."""
+    2 stores (1 - mix) v + mix v_first instead of v.  `q_norm` / `k_norm` [d] float32: every query / key head is divided
+    by its root mean square (`norm_eps` inside the root) and multiplied by the weight first (not together with blending)."""
     tokens = proj.shape[0]
     width = nq * d + nkv * d + nkv * e
     _need(proj, torch.float32, "qkv projection", (tokens, width + (nq if gate_out is not None else 0)))
@@ -1099,10 +1101,16 @@ def qkv_bias_store(proj: torch.Tensor, bias: torch.Tensor | None, q_out: torch.T
         _need(v_first, torch.float32, "v_first", (tokens, nkv * e))
     if gate_out is not None:
         _need(gate_out, torch.float32, "gate", (tokens, nq))
+    for w in (q_norm, k_norm):
+        if w is not None:
+            _need(w, torch.float32, "head norm weight", (d,))
+    if (q_norm is not None or k_norm is not None) and mix_mode:
+        raise InvalidRequest("qkv_bias_store: head norms together with blended values are not built")
     _check(hybrid_library().mrs_qkv_bias_store(_is_bf16(q_out.dtype), proj.data_ptr(), _ptr(bias), q_out.data_ptr(), _ptr(k_cache),
                                                _ptr(v_cache), _ptr(slots) if k_cache is not None else None, _ptr(v_first),
                                                _ptr(gate_out), tokens, nq, nkv, d, e, page_size, int(mix_mode), float(mix),
-                                               int(gate_out is not None), _stream()), "qkv_bias_store")
+                                               int(gate_out is not None), _ptr(q_norm), _ptr(k_norm), float(norm_eps), _stream()),
+           "qkv_bias_store")
 
 
 def gated_part_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, parts: int) -> None:
@@ -1132,7 +1140,7 @@ def biased_attention_library() -> ctypes.CDLL:
 
         lib = build()
         lib.mrs_attention_biased_simt.argtypes = [_c_int] + [_c_vp] * 9 + [_c_int] * 7 + [_c_float, _c_float, _c_int, _c_int, _c_int,
-                                                                                         _c_int, _c_vp]
+                                                                                         _c_int, _c_vp, _c_int, _c_vp]
         lib.mrs_attention_biased_simt.restype = _c_int
         _biased_simt_lib = lib
     return _biased_simt_lib
@@ -1140,9 +1148,11 @@ def biased_attention_library() -> ctypes.CDLL:
 
 def attention_biased_simt(q, k_cache, v_cache, positions, seq_of_token, block_table, out, nq: int, nkv: int, d: int, e: int,
                           scale: float, cap: float = 0.0, window: int = 0, keep_first: int = 0, bias: torch.Tensor | None = None,
-                          gate: torch.Tensor | None = None, sink: bool = False) -> None:
+                          gate: torch.Tensor | None = None, sink: bool = False, sink_logits: torch.Tensor | None = None,
+                          chunk: int = 0) -> None:
     """Causal paged attention with a soft cap on the scores, a bias by distance (`bias` float32 [rows, nq], the last row
-    for every larger distance), a window that keeps the first `keep_first` positions, an optional sink in the softmax
+    for every larger distance), a window that keeps the first `keep_first` positions or (`chunk` > 0, no window) sight
+    within the query's own chunk of positions, an optional sink in the softmax (its logit 0, or `sink_logits` [nq] float32)
     and an optional gate a (token, head); keys of d and values of e elements.  `v_cache` None: the values are the first
     e elements of the key rows.  One warp per (token, head)."""
     tokens = q.shape[0]
@@ -1167,11 +1177,13 @@ def attention_biased_simt(q, k_cache, v_cache, positions, seq_of_token, block_ta
             raise InvalidRequest("attention: the distance bias must be [rows, query heads]")
     if gate is not None:
         _need(gate, torch.float32, "attention gate", (tokens, nq))
+    if sink_logits is not None:
+        _need(sink_logits, torch.float32, "sink logits", (nq,))
     _check(biased_attention_library().mrs_attention_biased_simt(
         _is_bf16(q.dtype), q.data_ptr(), k_cache.data_ptr(), _ptr(v_cache), positions.data_ptr(), seq_of_token.data_ptr(),
         block_table.data_ptr(), _ptr(bias), _ptr(gate), out.data_ptr(), tokens, nq, nkv, d, e, page_size, block_table.shape[1],
-        float(scale), float(cap), int(window), int(keep_first), bias.shape[0] if bias is not None else 0, int(sink), _stream()),
-        "attention_biased_simt")
+        float(scale), float(cap), int(window), int(keep_first), bias.shape[0] if bias is not None else 0,
+        int(sink or sink_logits is not None), _ptr(sink_logits), int(chunk), _stream()), "attention_biased_simt")
 
 
 def causal_conv_silu(proj: torch.Tensor, offset: int, weight: torch.Tensor, bias: torch.Tensor | None, conv_state: torch.Tensor,
@@ -1279,7 +1291,7 @@ def attention_biased_mma_library(d: int, e: int, values_in_keys: bool = False) -
             defines["MRS_VALUES_IN_KEYS"] = 1
         lib = specialised_kernel_library("attention_biased_mma.cu", defines)
         lib.mrs_attention_biased_mma.argtypes = [_c_int] + [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_vp, _c_int,
-                                                 _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_vp]
+                                                 _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_vp]
         lib.mrs_attention_biased_mma.restype = _c_int
         lib.mrs_attention_biased_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.mrs_attention_biased_mma_scratch_floats.restype = ctypes.c_longlong
@@ -1289,7 +1301,8 @@ def attention_biased_mma_library(d: int, e: int, values_in_keys: bool = False) -
 
 def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int, e: int, scale: float,
                          cap: float = 0.0, window: int = 0, keep_first: int = 0, bias: torch.Tensor | None = None,
-                         gate: torch.Tensor | None = None, sink: bool = False, narrow: bool = False, splits: int = 1) -> None:
+                         gate: torch.Tensor | None = None, sink: bool = False, narrow: bool = False, splits: int = 1,
+                         sink_logits: torch.Tensor | None = None, chunk: int = 0) -> None:
     """`attention_biased_simt`'s formulas on the tensor cores, bfloat16, over a list of tiles (sequence, first row, tokens, 0):
     `narrow` tiles hold up to 16 // (nq // nkv) tokens (decoded tokens, short portions), the others up to 64 // (nq // nkv).
     `splits` > 1 (narrow tiles): that many CTAs share a tile's key blocks and a second kernel merges them.
@@ -1315,6 +1328,8 @@ def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out
             raise InvalidRequest("attention: the distance bias must be [rows, query heads]")
     if gate is not None:
         _need(gate, torch.float32, "attention gate", (tokens, nq))
+    if sink_logits is not None:
+        _need(sink_logits, torch.float32, "sink logits", (nq,))
     lib = attention_biased_mma_library(d, e, values_in_keys=v_cache is None)
     scratch = None
     if splits > 1:
@@ -1325,8 +1340,8 @@ def attention_biased_mma(q, k_cache, v_cache, positions, block_table, tiles, out
     _check(lib.mrs_attention_biased_mma(int(narrow), q.data_ptr(), k_cache.data_ptr(), _ptr(v_cache), positions.data_ptr(),
                                         block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(), tiles.shape[0], out.data_ptr(),
                                         _ptr(bias), bias.shape[0] if bias is not None else 0, _ptr(gate), nq, nkv, page_size,
-                                        float(scale), float(cap), int(window), int(keep_first), int(sink), int(splits), _ptr(scratch),
-                                        _stream()),
+                                        float(scale), float(cap), int(window), int(keep_first), int(sink or sink_logits is not None),
+                                        int(splits), _ptr(scratch), _ptr(sink_logits), int(chunk), _stream()),
            "attention_biased_mma")
 
 
@@ -1337,7 +1352,11 @@ _LATENT_SIGNATURES = {
     "mrs_add_layernorm": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_latent_prepare": [_c_int, _c_vp, _c_int, _c_vp, _c_float, _c_vp, _c_float, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp] +
                           [_c_int] * 8 + [_c_vp],
+    "mrs_latent_norms": [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_float, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_sigmoid_gate_mul": [_c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_scale": [_c_vp, ctypes.c_longlong, _c_float, _c_vp],
+}
+_EXPERT_SIGNATURES = {
     "mrs_moe_route": [_c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_vp],
     "mrs_moe_align": [_c_vp, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_vp],
     "mrs_moe_product_simt": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
@@ -1347,6 +1366,15 @@ _LATENT_SIGNATURES = {
     "mrs_moe_combine": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
 }
 _latent_lib = None
+_expert_lib = None
+
+
+def _typed(lib, signatures: dict):
+    for name, argtypes in signatures.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = _c_int
+    return lib
 
 
 def latent_library() -> ctypes.CDLL:
@@ -1356,18 +1384,25 @@ def latent_library() -> ctypes.CDLL:
             raise BackendError("no CUDA device: the engine has no CPU path")
         from .csrc.build import latent_kernel_library
 
-        lib = latent_kernel_library()
-        for name, argtypes in _LATENT_SIGNATURES.items():
-            fn = getattr(lib, name)
-            fn.argtypes = argtypes
-            fn.restype = _c_int
+        _latent_lib = _typed(latent_kernel_library(), _LATENT_SIGNATURES)
+    return _latent_lib
+
+
+def expert_library() -> ctypes.CDLL:
+    global _expert_lib
+    if _expert_lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        from .csrc.build import expert_kernel_library
+
+        lib = _typed(expert_kernel_library(), _EXPERT_SIGNATURES)
         lib.mrs_moe_capacity.argtypes = [_c_int, _c_int, _c_int]
         lib.mrs_moe_capacity.restype = ctypes.c_longlong
         for name in ("mrs_moe_simt_tile", "mrs_moe_mma_tile", "mrs_moe_rows_tile"):
             getattr(lib, name).argtypes = []
             getattr(lib, name).restype = _c_int
-        _latent_lib = lib
-    return _latent_lib
+        _expert_lib = lib
+    return _expert_lib
 
 
 def add_layernorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor, eps: float,
@@ -1430,6 +1465,40 @@ def latent_prepare(proj: torch.Tensor, latent_weight: torch.Tensor | None, eps: 
         tokens, heads, plain, rotated, latent, rotary, int(has_latent), int(gate is not None), _stream()), "latent_prepare")
 
 
+def latent_norms(proj: torch.Tensor, q_weight: torch.Tensor, latent_weight: torch.Tensor, eps: float, slots: torch.Tensor | None,
+                 q_latent: torch.Tensor, cache: torch.Tensor | None) -> None:
+    """After the fused float32 projection query latent | key/value latent | ... of a latent attention that rotates nothing:
+    `q_latent` [tokens, q_rank] gets the first columns over their root mean square times `q_weight`; the next `latent`
+    columns, normed likewise with `latent_weight`, go into `cache` [pages, 1, page, latent] at `slots` (None, or a slot of
+    -1: nowhere)."""
+    tokens, width = proj.shape
+    q_rank, latent = q_weight.shape[0], latent_weight.shape[0]
+    _need(proj, torch.float32, "latent projection")
+    if width < q_rank + latent:
+        raise InvalidRequest("latent_norms: the projection is narrower than the two latents")
+    _need(q_weight, torch.float32, "query latent norm weight", (q_rank,))
+    _need(latent_weight, torch.float32, "latent norm weight", (latent,))
+    _need(q_latent, None, "query latent", (tokens, q_rank))
+    if cache is not None:
+        _need(cache, q_latent.dtype, "latent pages")
+        if cache.dim() != 4 or cache.shape[1] != 1 or cache.shape[3] != latent:
+            raise InvalidRequest("latent_norms: the pages must be [pages, 1, page, latent]")
+        _need(slots, torch.int32, "slots", (tokens,))
+    _check(latent_library().mrs_latent_norms(_is_bf16(q_latent.dtype), proj.data_ptr(), width, q_weight.data_ptr(), latent_weight.data_ptr(),
+                                             float(eps), _ptr(slots) if cache is not None else None, q_latent.data_ptr(), _ptr(cache),
+                                             tokens, q_rank, latent, _stream()), "latent_norms")
+
+
+def sigmoid_gate_mul(x: torch.Tensor, gate: torch.Tensor) -> None:
+    """x <- x * sigmoid(gate), element by element, in place; `gate` float32 of x's shape, may be a column range of wider rows."""
+    tokens, width = x.shape
+    _need(x, None, "gated rows")
+    if not gate.is_cuda or gate.dtype != torch.float32 or tuple(gate.shape) != (tokens, width) or gate.stride(1) != 1:
+        raise InvalidRequest("sigmoid_gate_mul: the gate must be float32 of the rows' shape with unit column stride")
+    _check(latent_library().mrs_sigmoid_gate_mul(_is_bf16(x.dtype), x.data_ptr(), gate.data_ptr(), gate.stride(0), tokens, width,
+                                                 _stream()), "sigmoid_gate_mul")
+
+
 def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, chosen: torch.Tensor, weights: torch.Tensor,
               shared_gate: torch.Tensor | None, experts: int, top: int, scale: float, sigmoid_scores: bool = False) -> None:
     """Router logits float32 [tokens, experts (+ 1) or more] -> `chosen` [tokens, top] int32, the `top` experts with the
@@ -1446,26 +1515,26 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, chosen: tor
     _need(weights, torch.float32, "expert weights", (tokens, top))
     if shared_gate is not None:
         _need(shared_gate, torch.float32, "shared gate", (tokens,))
-    _check(latent_library().mrs_moe_route(logits.data_ptr(), logits.shape[1], _ptr(correction), chosen.data_ptr(), weights.data_ptr(),
+    _check(expert_library().mrs_moe_route(logits.data_ptr(), logits.shape[1], _ptr(correction), chosen.data_ptr(), weights.data_ptr(),
                                           _ptr(shared_gate), tokens, experts, top, float(scale), int(sigmoid_scores),
                                           int(shared_gate is not None), _stream()), "moe_route")
 
 
 def moe_capacity(pairs: int, routed: int, tile: int) -> int:
     """Rows of the expert lists for `pairs` (token, choice) pairs: every expert's run filled up to whole tiles."""
-    return int(latent_library().mrs_moe_capacity(pairs, routed, tile))
+    return int(expert_library().mrs_moe_capacity(pairs, routed, tile))
 
 
 def moe_simt_tile() -> int:
-    return int(latent_library().mrs_moe_simt_tile())
+    return int(expert_library().mrs_moe_simt_tile())
 
 
 def moe_mma_tile() -> int:
-    return int(latent_library().mrs_moe_mma_tile())
+    return int(expert_library().mrs_moe_mma_tile())
 
 
 def moe_rows_tile() -> int:
-    return int(latent_library().mrs_moe_rows_tile())
+    return int(expert_library().mrs_moe_rows_tile())
 
 
 def moe_rows_supported(x: torch.Tensor, inner: int) -> bool:
@@ -1486,7 +1555,7 @@ def moe_align(chosen: torch.Tensor, routed: int, tile: int, sorted_rows: torch.T
     _need(chosen, torch.int32, "chosen experts")
     _need(sorted_rows, torch.int32, "sorted rows")
     _need(tile_expert, torch.int32, "tile experts", (sorted_rows.shape[0] // tile + 1,))
-    _check(latent_library().mrs_moe_align(chosen.data_ptr(), chosen.numel(), routed, tile, sorted_rows.data_ptr(), tile_expert.data_ptr(),
+    _check(expert_library().mrs_moe_align(chosen.data_ptr(), chosen.numel(), routed, tile, sorted_rows.data_ptr(), tile_expert.data_ptr(),
                                           sorted_rows.shape[0], _stream()), "moe_align")
 
 
@@ -1508,18 +1577,18 @@ def moe_product(x: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.T
         raise InvalidRequest("moe_product: the listed rows do not match the lists")
     if kernel == "mma":
         _need(x, torch.bfloat16, "expert input")
-        _check(latent_library().mrs_moe_product_mma(int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
+        _check(expert_library().mrs_moe_product_mma(int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
                                                     weight.data_ptr(), out.data_ptr(), capacity, n, k, top, int(block) if gated else 0,
                                                     _stream()), "moe_product_mma")
         return
     if kernel == "rows":
-        _check(latent_library().mrs_moe_product_rows(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(),
+        _check(expert_library().mrs_moe_product_rows(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(),
                                                      tile_expert.data_ptr(), weight.data_ptr(), out.data_ptr(), capacity, n, k, top,
                                                      int(block) if gated else 0, _stream()), "moe_product_rows")
         return
     if kernel != "simt":
         raise InvalidRequest(f"moe_product: unknown kernel {kernel!r}")
-    _check(latent_library().mrs_moe_product_simt(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
+    _check(expert_library().mrs_moe_product_simt(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
                                                  weight.data_ptr(), out.data_ptr(), capacity, n, k, top, int(block) if gated else 0,
                                                  _stream()), "moe_product_simt")
 
@@ -1600,7 +1669,7 @@ def moe_gather_rows(x: torch.Tensor, sorted_rows: torch.Tensor, out: torch.Tenso
     """out[place] = x[pair / top] for every listed pair, zeros where a run is filled up (bfloat16, rows of a multiple of 8)."""
     _need(x, torch.bfloat16, "expert input")
     _need(out, torch.bfloat16, "gathered rows", (sorted_rows.shape[0], x.shape[1]))
-    _check(latent_library().mrs_moe_gather_rows(x.data_ptr(), sorted_rows.data_ptr(), out.data_ptr(), out.shape[0], x.shape[1], top,
+    _check(expert_library().mrs_moe_gather_rows(x.data_ptr(), sorted_rows.data_ptr(), out.data_ptr(), out.shape[0], x.shape[1], top,
                                                 _stream()), "moe_gather_rows")
 
 
@@ -1657,5 +1726,135 @@ def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tenso
     if shared_out is not None:
         _need(shared_out, h.dtype, "shared expert output", (tokens, width))
         _need(shared_gate, torch.float32, "shared gate", (tokens,))
-    _check(latent_library().mrs_moe_combine(_is_bf16(h.dtype), _ptr(y), h.data_ptr(), _ptr(shared_out), chosen.data_ptr(), weights.data_ptr(),
+    _check(expert_library().mrs_moe_combine(_is_bf16(h.dtype), _ptr(y), h.data_ptr(), _ptr(shared_out), chosen.data_ptr(), weights.data_ptr(),
                                             _ptr(shared_gate), out.data_ptr(), tokens, width, top, routed, _stream()), "moe_combine")
+
+
+# ------------------------------------------------------------------------------------------------
+# branches side by side, plain feed-forwards, capped logits; the gated delta rule
+# ------------------------------------------------------------------------------------------------
+_PARALLEL_SIGNATURES = {
+    "mrs_add_branches_norm": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_activation": [_c_int, _c_vp, _c_vp, ctypes.c_longlong, _c_int, _c_vp],
+    "mrs_scale_softcap": [_c_vp, ctypes.c_longlong, _c_float, _c_float, _c_vp],
+}
+_DELTA_SIGNATURES = {
+    "mrs_delta_prepare": [_c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                          _c_float, _c_vp],
+    "mrs_delta_scan": [_c_vp, _c_vp, _c_vp, ctypes.c_longlong, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_vp],
+    "mrs_head_norm_gate": [_c_int, _c_vp, _c_vp, _c_int, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_int, _c_vp],
+}
+_parallel_lib = None
+_delta_lib = None
+ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def parallel_library() -> ctypes.CDLL:
+    global _parallel_lib
+    if _parallel_lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        from .csrc.build import parallel_kernel_library
+
+        _parallel_lib = _typed(parallel_kernel_library(), _PARALLEL_SIGNATURES)
+    return _parallel_lib
+
+
+def delta_library() -> ctypes.CDLL:
+    global _delta_lib
+    if _delta_lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        from .csrc.build import delta_kernel_library
+
+        _delta_lib = _typed(delta_kernel_library(), _DELTA_SIGNATURES)
+    return _delta_lib
+
+
+def add_branches_norm(stream: torch.Tensor, a: torch.Tensor, b: torch.Tensor | None, next_weight: torch.Tensor | None,
+                      next_eps: float, out: torch.Tensor | None) -> None:
+    """stream += a (+ b), all float32 [rows, width]; with `next_weight`, out = stream / sqrt(mean(stream^2) + eps) * next_weight
+    in out's dtype."""
+    rows, width = stream.shape
+    _need(stream, torch.float32, "stream")
+    _need(a, torch.float32, "branch", (rows, width))
+    if b is not None:
+        _need(b, torch.float32, "second branch", (rows, width))
+    if next_weight is not None:
+        _need(next_weight, torch.float32, "next norm weight", (width,))
+        _need(out, None, "normed rows", (rows, width))
+    _check(parallel_library().mrs_add_branches_norm(_is_bf16(out.dtype) if out is not None and next_weight is not None else 0,
+                                                    stream.data_ptr(), a.data_ptr(), _ptr(b), _ptr(next_weight), float(next_eps),
+                                                    _ptr(out) if next_weight is not None else None, rows, width, _stream()),
+           "add_branches_norm")
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out = act(x) element by element (float32 arithmetic): "gelu_erf" 0.5 z (1 + erf(z / sqrt 2)), "gelu_tanh"
+    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), "silu"."""
+    if kind not in ACTIVATIONS:
+        raise InvalidRequest(f"activation {kind!r} is not built; known: {sorted(ACTIVATIONS)}")
+    _need(x, None, "activation input")
+    _need(out, x.dtype, "activation output", tuple(x.shape))
+    _check(parallel_library().mrs_activation(_is_bf16(x.dtype), x.data_ptr(), out.data_ptr(), x.numel(), ACTIVATIONS[kind], _stream()),
+           "activation")
+
+
+def scale_softcap_(x: torch.Tensor, scale: float, cap: float) -> None:
+    """x <- cap * tanh(x * scale / cap), float32, in place."""
+    _need(x, torch.float32, "capped tensor")
+    if not cap > 0:
+        raise InvalidRequest("a soft cap must be positive")
+    _check(parallel_library().mrs_scale_softcap(x.data_ptr(), x.numel(), float(scale), float(cap), _stream()), "scale_softcap")
+
+
+def delta_prepare(qkv: torch.Tensor, raw: torch.Tensor, b_offset: int, a_offset: int, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                  coef: torch.Tensor, groups: int, d: int, heads: int, e: int, unit_eps: float, q_factor: float) -> None:
+    """Per token, in place on `qkv` [tokens, 2 * groups * d + heads * e] float32 (q of every group | k of every group | v of
+    every head): every q and k becomes x / sqrt(sum x^2 + unit_eps), q also times `q_factor`; `coef` [tokens, 2 * heads]
+    gets beta = sigmoid(b) and g = exp(-exp(A_log) * softplus(a + dt_bias)) of every head, b and a read at the columns
+    `b_offset` and `a_offset` of the float32 rows `raw`."""
+    tokens = qkv.shape[0]
+    _need(qkv, torch.float32, "q|k|v", (tokens, 2 * groups * d + heads * e))
+    _need(raw, torch.float32, "delta projection")
+    if raw.shape[0] != tokens or min(b_offset, a_offset) < 0 or max(b_offset, a_offset) + heads > raw.shape[1]:
+        raise InvalidRequest("delta_prepare: b and a lie outside the rows")
+    _need(a_log, torch.float32, "A_log", (heads,))
+    _need(dt_bias, torch.float32, "dt_bias", (heads,))
+    _need(coef, torch.float32, "beta|g", (tokens, 2 * heads))
+    _check(delta_library().mrs_delta_prepare(qkv.data_ptr(), raw.data_ptr(), raw.shape[1], int(b_offset), int(a_offset), a_log.data_ptr(),
+                                             dt_bias.data_ptr(), coef.data_ptr(), tokens, groups, d, heads, e, float(unit_eps),
+                                             float(q_factor), _stream()), "delta_prepare")
+
+
+def delta_scan(qkv: torch.Tensor, coef: torch.Tensor, state: torch.Tensor, positions, q_start, state_slots, out: torch.Tensor,
+               heads: int, groups: int, d: int, e: int, write_state: bool = True) -> None:
+    """The gated delta rule token by token, float32, per (sequence, head): S <- g S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  `qkv` as `delta_prepare` leaves it, `coef` its beta | g; `state` [slots, heads, d, e] float32 (a view: dense
+    within a slot); a sequence that starts at position 0 starts from zero; `out` [tokens, heads * e] float32."""
+    tokens = qkv.shape[0]
+    _need(qkv, torch.float32, "q|k|v", (tokens, 2 * groups * d + heads * e))
+    _need(coef, torch.float32, "beta|g", (tokens, 2 * heads))
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, d, e) or state.stride(3) != 1 or state.stride(2) != e or \
+            state.stride(1) != d * e:
+        raise InvalidRequest("delta_scan: the state must be float32 [slots, heads, d, e], dense within a slot")
+    _need(out, torch.float32, "recurrence output", (tokens, heads * e))
+    sequences = state_slots.shape[0]
+    _check(delta_library().mrs_delta_scan(qkv.data_ptr(), coef.data_ptr(), state.data_ptr(), state.stride(0), positions.data_ptr(),
+                                          q_start.data_ptr(), state_slots.data_ptr(), out.data_ptr(), tokens, sequences, heads, groups,
+                                          d, e, int(write_state), _stream()), "delta_scan")
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, heads: int) -> None:
+    """out = o / sqrt(mean over a head of o^2 + eps) * weight * silu(gate): `o` float32 [tokens, heads * e], `weight` [e]
+    float32 shared by the heads, `gate` float32 of o's shape (may be a column range of wider rows)."""
+    tokens, inner = o.shape
+    e = inner // heads
+    _need(o, torch.float32, "recurrence output")
+    if not gate.is_cuda or gate.dtype != torch.float32 or tuple(gate.shape) != (tokens, inner) or gate.stride(1) != 1:
+        raise InvalidRequest("head_norm_gate: the gate must be float32 [tokens, heads * e] with unit column stride")
+    _need(weight, torch.float32, "head norm weight", (e,))
+    _need(out, None, "head norm out", (tokens, inner))
+    _check(delta_library().mrs_head_norm_gate(_is_bf16(out.dtype), o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(),
+                                              float(eps), out.data_ptr(), tokens, heads, e, _stream()), "head_norm_gate")

@@ -8,9 +8,10 @@ import os
 from dataclasses import dataclass
 from typing import Callable
 
-from ..config.model_config import ModelConfig, NiduvikConfig, Qwen3Config, SatedraConfig
+from ..config.model_config import ModelConfig, NiduvikConfig, NubipelConfig, Qwen3Config, SatedraConfig
 from ..errors import InvalidRequest
 from .niduvik import niduvik_spec
+from .nubipel import nubipel_spec
 from .qwen3 import qwen3_spec
 from .satedra import satedra_spec
 from .spec import ModelSpec
@@ -35,6 +36,7 @@ def register_architecture(model_type: str, config_class: type, spec: Callable[[M
 register_architecture("qwen3", Qwen3Config, qwen3_spec)
 register_architecture("niduvik", NiduvikConfig, niduvik_spec)
 register_architecture("satedra", SatedraConfig, satedra_spec)
+register_architecture("nubipel", NubipelConfig, nubipel_spec)
 
 
 def config_from_dict(raw: dict) -> ModelConfig:

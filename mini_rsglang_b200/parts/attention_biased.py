@@ -5,8 +5,11 @@
   * a soft cap on the scaled scores, cap * tanh(score / cap), and after it a learned bias by the distance
     i - j, taken from a small table through buckets: one row a distance below half the table, then rows spaced
     evenly in the logarithm of the distance up to `bias_far`, the last row for everything beyond;
-  * a sliding window that also keeps the first `keep_first` positions in sight (at their true distances);
-  * a softmax with a sink: one more term of score 0 and no value in the denominator;
+  * a sliding window that also keeps the first `keep_first` positions in sight (at their true distances); or sight in
+    chunks: position i sees j <= i only where floor(i / chunk) = floor(j / chunk), chunks counted from position 0;
+  * an RMS norm over every query and key head (one weight of the head's size for all query heads, one for all key heads);
+  * a softmax with a sink: one more term in the denominator that has no key and no value, exp(0) or exp of a learned
+    number a head (not scaled);
   * values blended with those of the first layer that blends, (1 - m) v + m v_first per token; the blended values
     are what the cache holds;
   * an output gate, one sigmoid a (token, head), from the same input as the projections.
@@ -55,8 +58,11 @@ class BiasedWindowAttention(Mixer):
                  scale: float | None = None, softcap: float = 0.0, window: int = 0, keep_first: int = 0,
                  bias_rows: int = 0, bias_far: float = 0.0, sink: bool = False, projection_bias: bool = False,
                  value_mix: str | None = None, value_mix_source: bool = False, output_gate: bool = False,
+                 chunk: int = 0, sink_logits: bool = False, head_norm_eps: float | None = None,
                  names: dict | None = None):
-        """`value_mix`: a key under which the layers that blend values find the first one's values within a step
+        """`chunk` > 0 (no window then): sight within the query's chunk of positions.  `sink_logits`: the sink's logit is a
+        learned number a query head.  `head_norm_eps`: query and key heads pass an RMS norm with this epsilon (None: no norm).
+        `value_mix`: a key under which the layers that blend values find the first one's values within a step
         (None: no blending); `value_mix_source`: this layer is that first one (its own mixing weight is unused).
         `names`: leaves of the tensors below the part's root."""
         super().__init__(prefix)
@@ -69,8 +75,15 @@ class BiasedWindowAttention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.d)
         self.softcap, self.window, self.keep_first = float(softcap), int(window), int(keep_first)
         self.bias_rows, self.bias_far, self.sink = int(bias_rows), float(bias_far), bool(sink)
-        if self.window < 0 or self.keep_first < 0 or self.softcap < 0:
-            raise InvalidRequest("window, kept first positions and soft cap cannot be negative")
+        self.chunk, self.sink_logits = int(chunk), bool(sink_logits)
+        self.head_norm_eps = None if head_norm_eps is None else float(head_norm_eps)
+        self.sink = self.sink or self.sink_logits
+        if self.window < 0 or self.keep_first < 0 or self.softcap < 0 or self.chunk < 0:
+            raise InvalidRequest("window, chunk, kept first positions and soft cap cannot be negative")
+        if self.chunk and (self.window or self.keep_first):
+            raise InvalidRequest("sight in chunks together with a window or kept first positions is not built")
+        if self.head_norm_eps is not None and value_mix:
+            raise InvalidRequest("head norms together with blended values are not built")
         # bias_rows -1: as many rows as the checkpoint's table has
         if self.bias_rows > 0:
             self._check_bias_table(self.bias_rows)
@@ -78,9 +91,10 @@ class BiasedWindowAttention(Mixer):
         self.value_mix, self.value_mix_source = value_mix, bool(value_mix_source)
         self.leaf = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "bias_table": "distance_bias",
-                     "mix": "value_mix", "gate": "gate_proj.weight"}
+                     "mix": "value_mix", "gate": "gate_proj.weight", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight",
+                     "sink": "sinks"}
         self.leaf.update(names or {})
-        self.fused = self.o = self.bias = self.distance_bias = None
+        self.fused = self.o = self.bias = self.distance_bias = self.q_norm = self.k_norm = self.sinks = None
         self.mix = 0.0
         self._plan_arguments = None
 
@@ -104,10 +118,17 @@ class BiasedWindowAttention(Mixer):
             specs.append(WeightSpec(self.name(n["mix"]), (), "bias"))
         if self.output_gate:
             specs.append(WeightSpec(self.name(n["gate"]), (self.nq, self.width)))
+        if self.head_norm_eps is not None:
+            specs += [WeightSpec(self.name(n["q_norm"]), (self.d,), "vector"), WeightSpec(self.name(n["k_norm"]), (self.d,), "vector")]
+        if self.sink_logits:
+            specs.append(WeightSpec(self.name(n["sink"]), (self.nq,), "bias"))
         return specs
 
     def cache_need(self):
-        # a window gives passed pages back; the pages of kept first positions stay with the request
+        # a window gives passed pages back; the pages of kept first positions stay with the request; a chunk never
+        # reaches further back than its own length, so its cache is a window of that many keys
+        if self.chunk:
+            return KVNeed(self.nkv, self.d, "window", self.chunk, value_dim=self.e)
         if self.window:
             return KVNeed(self.nkv, self.d, "window", self.window, value_dim=self.e, keep_first=self.keep_first)
         return KVNeed(self.nkv, self.d, "full", 0, value_dim=self.e)
@@ -129,6 +150,11 @@ class BiasedWindowAttention(Mixer):
             self.distance_bias = table[rows_of].contiguous()         # [distances, heads]: the table, a row a distance
         if self.value_mix and not self.value_mix_source:
             self.mix = float(tensors[self.name(n["mix"])].float().item())
+        if self.head_norm_eps is not None:
+            self.q_norm = tensors[self.name(n["q_norm"])].float().contiguous()
+            self.k_norm = tensors[self.name(n["k_norm"])].float().contiguous()
+        if self.sink_logits:
+            self.sinks = tensors[self.name(n["sink"])].float().contiguous()
 
     def forward(self, h, ctx, cache, write_cache=True):
         tokens = h.shape[0]
@@ -148,7 +174,8 @@ class BiasedWindowAttention(Mixer):
                 v_first, mode = ctx.shared[key], 2
         kernels.qkv_bias_store(proj, self.bias, q, cache.k if write_cache else None, cache.v if write_cache else None,
                                ctx.slots[cache.group] if write_cache else None, self.nq, self.nkv, self.d, self.e,
-                               v_first=v_first, mix_mode=mode, mix=self.mix, gate_out=gate)
+                               v_first=v_first, mix_mode=mode, mix=self.mix, gate_out=gate, q_norm=self.q_norm, k_norm=self.k_norm,
+                               norm_eps=self.head_norm_eps or 0.0)
         out = torch.empty((tokens, self.nq * self.e), dtype=dtype, device=device)
         table = ctx.block_tables[cache.group]
         arguments = self._tile_plan()
@@ -156,7 +183,7 @@ class BiasedWindowAttention(Mixer):
             # the 32-bit path and head sizes that the tensor-core kernel does not take: one warp a (token, head)
             kernels.attention_biased_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, table, out, self.nq, self.nkv,
                                           self.d, self.e, self.scale, self.softcap, self.window, self.keep_first,
-                                          self.distance_bias, gate, self.sink)
+                                          self.distance_bias, gate, self.sink, self.sinks, self.chunk)
         else:
             # decoded tokens and short portions in tiles of 16 rows whose warps share the keys, longer portions in tiles of 64
             narrow, wide, longest, _ = plan_attention_tiles(ctx, *arguments)
@@ -164,11 +191,11 @@ class BiasedWindowAttention(Mixer):
                 if tiles is not None:
                     splits = 1
                     if is_narrow:          # few rows: the keys in sight (the window and the kept tokens at most) are shared among CTAs
-                        reach = min(longest, self.window + self.keep_first) if self.window else longest
+                        reach = min(longest, self.window + self.keep_first) if self.window else (min(longest, self.chunk) if self.chunk else longest)
                         splits = min(choose_splits(tiles.shape[0], self.nkv, reach, arguments[5]), 16)
                     kernels.attention_biased_mma(q, cache.k, cache.v, ctx.positions, table, tiles, out, self.nq, self.nkv, self.d,
                                                  self.e, self.scale, self.softcap, self.window, self.keep_first, self.distance_bias,
-                                                 gate, self.sink, narrow=is_narrow, splits=splits)
+                                                 gate, self.sink, narrow=is_narrow, splits=splits, sink_logits=self.sinks, chunk=self.chunk)
         return linear(out, self.o, out_dtype=torch.float32)
 
     def _tile_plan(self) -> tuple:
@@ -178,7 +205,7 @@ class BiasedWindowAttention(Mixer):
             if self.runtime.dtype is torch.bfloat16 and \
                     kernels.attention_biased_mma_supported(self.d, self.e, group, self.runtime.page_size):
                 # the window enters the plan only as the reach of a tile's keys; kept first tokens add a block at most
-                self._plan_arguments = (group, kernels.MMA_ROWS_WIDE, self.nkv, self.window, 128, kernels.sm_count(self.o.device))
+                self._plan_arguments = (group, kernels.MMA_ROWS_WIDE, self.nkv, self.window or self.chunk, 128, kernels.sm_count(self.o.device))
             else:
                 self._plan_arguments = ()
         return self._plan_arguments

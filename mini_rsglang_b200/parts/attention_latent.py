@@ -18,7 +18,11 @@ sum_j p_j W_uv c_j = W_uv sum_j p_j c_j, a head's query becomes [W_uk^T q_plain 
 another layer that keeps one (`shares_cache`): it has no W_dkv, and uses that layer's rows with its own W_uk and
 W_uv, queries, window and gate.
 
-One projection gives q | c', k_r | gates as float32 sums; one kernel norms the latent, rotates, gates and writes the
+The queries may pass a latent of their own (`query_latent_dim`): c_q = W_dq h / rms(W_dq h) * w_q, q = W_uq c_q; such a layer
+rotates nothing here.  The gate is one sigmoid a (token, head), or (`output_gate="elements"`) one a (token, head, value
+element), W_g then having heads * e rows.
+
+One projection gives q | c', k_r | gates (or c_q' | c' | gates) as float32 sums; one kernel norms the latent, rotates, gates and writes the
 cache row; a batched product carries the queries into the latent space; one kernel attends; a batched product and the
 output projection bring the heads back.  Every size and constant is a parameter."""
 from __future__ import annotations
@@ -39,11 +43,15 @@ class LatentAttention(Mixer):
 
     def __init__(self, prefix: str, width: int, num_heads: int, head_dim: int, rotary_head_dim: int, value_dim: int,
                  latent_dim: int, scale: float, eps: float, position: PartSpec | None = None, window: int = 0,
-                 cache_window: int | None = None, shares_cache: bool = False, output_gate: bool = False,
+                 cache_window: int | None = None, shares_cache: bool = False, output_gate: bool | str = False,
+                 query_latent_dim: int = 0, float32_out: bool = False,
                  names: dict | None = None):
         """`position`: the encoding of the rotated part (None: nothing turns).  `window` 0: every earlier key is seen.
         `cache_window`: the window that the cache is kept for, where other layers read this layer's cache with wider
         windows (0: every key).  `shares_cache`: this layer reads another layer's cache and has no down-projection.
+        `output_gate`: False, True or "heads" (one gate a head), or "elements" (one a value element of every head).
+        `query_latent_dim` > 0: the queries are made from a normed latent of that size.
+        `float32_out`: the output projection hands on its float32 sums (for a residual sum that reads them).
         `names`: leaves of the tensors below the part's root."""
         super().__init__(prefix)
         self.width, self.heads, self.d, self.r = int(width), int(num_heads), int(head_dim), int(rotary_head_dim)
@@ -56,12 +64,22 @@ class LatentAttention(Mixer):
         self.cache_window = self.window if cache_window is None else int(cache_window)
         if self.window < 0 or (self.cache_window and (not self.window or self.cache_window < self.window)):
             raise InvalidRequest(f"{prefix}: the cache must keep at least the keys that the layer's window sees")
+        if output_gate not in (False, True, "heads", "elements"):
+            raise InvalidRequest(f"{prefix}: output_gate must be False, True, \"heads\" or \"elements\"")
         self.shares_cache, self.output_gate = bool(shares_cache), bool(output_gate)
+        self.gate_elements = output_gate == "elements"
+        self.float32_out = bool(float32_out)
+        self.query_latent = int(query_latent_dim)
+        if self.query_latent < 0 or (self.query_latent and (self.r or self.shares_cache or position is not None)):
+            raise InvalidRequest(f"{prefix}: queries from a latent together with a rotated part or a borrowed cache are not built")
+        if self.gate_elements and not self.query_latent:
+            raise InvalidRequest(f"{prefix}: a gate a value element is built for layers whose queries pass a latent")
         self.position = POSITION_ENCODINGS.build(position, prefix) if position is not None else None
         self.leaf = {"q": "q_proj.weight", "down": "kv_down_proj.weight", "latent_norm": "kv_norm.weight", "up_k": "k_up_proj.weight",
-                     "up_v": "v_up_proj.weight", "gate": "gate_proj.weight", "o": "o_proj.weight"}
+                     "up_v": "v_up_proj.weight", "gate": "gate_proj.weight", "o": "o_proj.weight", "q_down": "q_down_proj.weight",
+                     "q_norm": "q_norm.weight", "q_up": "q_up_proj.weight"}
         self.leaf.update(names or {})
-        self.fused = self.latent_weight = self.up_k = self.up_v = self.o = None
+        self.fused = self.latent_weight = self.up_k = self.up_v = self.o = self.q_up = self.q_latent_weight = None
         self.rotation = None
         self._plan_arguments = None
 
@@ -72,14 +90,19 @@ class LatentAttention(Mixer):
 
     def weight_specs(self):
         n = self.leaf
-        specs = [WeightSpec(self.name(n["q"]), (self.heads * (self.d + self.r), self.width))]
+        if self.query_latent:
+            specs = [WeightSpec(self.name(n["q_down"]), (self.query_latent, self.width)),
+                     WeightSpec(self.name(n["q_norm"]), (self.query_latent,), "vector"),
+                     WeightSpec(self.name(n["q_up"]), (self.heads * self.d, self.query_latent))]
+        else:
+            specs = [WeightSpec(self.name(n["q"]), (self.heads * (self.d + self.r), self.width))]
         if not self.shares_cache:
             specs += [WeightSpec(self.name(n["down"]), (self.row, self.width)),
                       WeightSpec(self.name(n["latent_norm"]), (self.latent,), "vector")]
         specs += [WeightSpec(self.name(n["up_k"]), (self.heads * self.d, self.latent)),
                   WeightSpec(self.name(n["up_v"]), (self.heads * self.e, self.latent))]
         if self.output_gate:
-            specs.append(WeightSpec(self.name(n["gate"]), (self.heads, self.width)))
+            specs.append(WeightSpec(self.name(n["gate"]), (self.heads * self.e if self.gate_elements else self.heads, self.width)))
         specs.append(WeightSpec(self.name(n["o"]), (self.width, self.heads * self.e)))
         return specs
 
@@ -90,7 +113,10 @@ class LatentAttention(Mixer):
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
         n = self.leaf
-        rows = [tensors[self.name(n["q"])]]
+        rows = [tensors[self.name(n["q_down" if self.query_latent else "q"])]]
+        if self.query_latent:
+            self.q_latent_weight = tensors[self.name(n["q_norm"])]
+            self.q_up = tensors[self.name(n["q_up"])].contiguous()
         if not self.shares_cache:
             rows.append(tensors[self.name(n["down"])])
             self.latent_weight = tensors[self.name(n["latent_norm"])]
@@ -113,15 +139,23 @@ class LatentAttention(Mixer):
         device, dtype = self.o.device, self.runtime.dtype
         H, R, row = self.heads, self.latent, self.row
         proj = linear(h, self.fused, out_dtype=torch.float32)
-        q_plain = torch.empty((H, tokens, self.d), dtype=dtype, device=device)
         q_rows = torch.empty((tokens, H, row), dtype=dtype, device=device)
-        gate = torch.empty((tokens, H), dtype=torch.float32, device=device) if self.output_gate else None
         keeps = write_cache and not self.shares_cache
-        rotation = self.rotation
-        kernels.latent_prepare(proj, self.latent_weight, self.eps, rotation.inv_freq if rotation else None,
-                               rotation.magnitude if rotation else 1.0, ctx.positions, ctx.slots[cache.group] if keeps else None,
-                               q_plain, q_rows, cache.k if keeps else None, gate, H, self.d, self.r, R,
-                               rotation.rotary_dim if rotation else 0, not self.shares_cache)
+        if self.query_latent:
+            # c_q' | c' | gates: both latents normed by one kernel, the second into the cache; then the queries' up-projection
+            q_latent = torch.empty((tokens, self.query_latent), dtype=dtype, device=device)
+            kernels.latent_norms(proj, self.q_latent_weight, self.latent_weight, self.eps, ctx.slots[cache.group] if keeps else None,
+                                 q_latent, cache.k if keeps else None)
+            q_plain = linear(q_latent, self.q_up).view(tokens, H, self.d).transpose(0, 1)
+            gate = None
+        else:
+            q_plain = torch.empty((H, tokens, self.d), dtype=dtype, device=device)
+            gate = torch.empty((tokens, H), dtype=torch.float32, device=device) if self.output_gate else None
+            rotation = self.rotation
+            kernels.latent_prepare(proj, self.latent_weight, self.eps, rotation.inv_freq if rotation else None,
+                                   rotation.magnitude if rotation else 1.0, ctx.positions, ctx.slots[cache.group] if keeps else None,
+                                   q_plain, q_rows, cache.k if keeps else None, gate, H, self.d, self.r, R,
+                                   rotation.rotary_dim if rotation else 0, not self.shares_cache)
         # the queries in the latent space: q_rows[:, head, :R] = q_plain[head] . W_uk[head]
         torch.bmm(q_plain, self.up_k, out=q_rows[:, :, :R].transpose(0, 1))
         q_rows = q_rows.view(tokens, H * row)
@@ -145,7 +179,13 @@ class LatentAttention(Mixer):
         # back to the heads' values: out[:, head] = mixed[:, head] . W_uv[head]^T
         out = torch.empty((tokens, H, self.e), dtype=dtype, device=device)
         torch.bmm(mixed.view(tokens, H, R).transpose(0, 1), self.up_v, out=out.transpose(0, 1))
-        return linear(out.view(tokens, H * self.e), self.o)
+        out = out.view(tokens, H * self.e)
+        if self.query_latent and self.output_gate:
+            gates = proj[:, self.query_latent + R:]
+            if not self.gate_elements:             # one gate a head: spread over the head's value elements
+                gates = gates.repeat_interleave(self.e, dim=1)
+            kernels.sigmoid_gate_mul(out, gates)
+        return linear(out, self.o, out_dtype=torch.float32 if self.float32_out else None)
 
     def _tile_plan(self) -> tuple:
         """What the tile planner is asked for this attention ((): no tiles, the CUDA-core kernel takes every row).  All

@@ -1,5 +1,6 @@
 """How a layer's parts are arranged.  "pre_norm": x + mixer(norm1(x)), then
-+ feed_forward(norm2(.)) (reference: crates/models/src/qwen3.rs:176-225).
++ feed_forward(norm2(.)) (reference: crates/models/src/qwen3.rs:176-225).  "sandwich_norm": a norm before and after
+each branch.  "parallel": both branches read one norm's output, x + (mixer(norm1(x)) + feed_forward(norm1(x))).
 
 The residual stream is float32.  A branch's output is not added by a kernel of its own: it
 is handed on as `pending`, and the next norm adds it while it reads the stream anyway; or,
@@ -109,3 +110,34 @@ class SandwichNormBlock(Block):
         if observing(ctx):
             ctx.observe(f"{ctx.label}-output", stream.clone())
         return pending
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(Block):
+    """Both branches side by side on one normed input: with h = norm1(x), x <- x + (mixer(h) + feed_forward(h)); a layer may
+    be a mixer alone.
+
+    The branches' last products leave float32 sums; one kernel adds both to the float32 stream and runs the norm that reads
+    the stream next (`kernels.add_branches_norm`), whose rows are handed on as a `Normed`: a layer is one norm launch."""
+
+    links_norms = True
+    roles = {"norm1": NORMS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS}
+    optional_roles = ("feed_forward",)
+    entry_role = "norm1"
+
+    def forward(self, stream, pending, ctx, cache, write_cache=True, next_norm=None):
+        h = plain(self.norm1.add_norm(stream, pending))
+        if observing(ctx):
+            ctx.observe(f"{ctx.label}-input_norm", h)
+        a = self.mixer.forward(h, ctx, cache, write_cache)
+        f = self.feed_forward.forward(h, ctx) if self.feed_forward is not None else None
+        if a.dtype is not torch.float32:          # a branch written for another arrangement
+            a = a.float()
+        if f is not None and f.dtype is not torch.float32:
+            f = f.float()
+        fused = next_norm is not None and getattr(next_norm, "rides_on_products", False) and not next_norm.gathers_rows
+        out = torch.empty(stream.shape, dtype=self.runtime.dtype, device=stream.device) if fused else None
+        kernels.add_branches_norm(stream, a, f, next_norm.weight if fused else None, next_norm.eps if fused else 0.0, out)
+        if observing(ctx):
+            ctx.observe(f"{ctx.label}-output", stream.clone())
+        return Normed(out, next_norm, stream) if fused else None

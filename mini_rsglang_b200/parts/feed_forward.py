@@ -97,3 +97,33 @@ class ClampedGLU(FeedForward):
         act = torch.empty((h.shape[0], self.inner), dtype=self.runtime.dtype, device=self.down.device)
         kernels.glu_clamped(linear(h, self.gate_up), act, self.limit, self.alpha)
         return linear(act, self.down, out_dtype=torch.float32)
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(FeedForward):
+    """A plain feed-forward without a gate: down(act(up(x))), act one of `kernels.ACTIVATIONS` ("gelu_erf": the exact
+    gelu 0.5 z (1 + erf(z / sqrt 2)); "gelu_tanh"; "silu"), computed in float32.  The result keeps the down product's
+    float32 sums (the residual sum that follows reads them)."""
+
+    def __init__(self, prefix: str, width: int, inner: int, activation: str = "gelu_erf", names: dict | None = None):
+        super().__init__(prefix)
+        if activation not in kernels.ACTIVATIONS:
+            raise InvalidRequest(f"activation {activation!r} is not built; known: {sorted(kernels.ACTIVATIONS)}")
+        self.width, self.inner, self.activation = int(width), int(inner), activation
+        self.leaf = {"up": "up_proj.weight", "down": "down_proj.weight"}
+        self.leaf.update(names or {})
+        self.up = self.down = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.name(self.leaf["up"]), (self.inner, self.width)),
+                WeightSpec(self.name(self.leaf["down"]), (self.width, self.inner))]
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.up = tensors[self.name(self.leaf["up"])].contiguous()
+        self.down = tensors[self.name(self.leaf["down"])].contiguous()
+
+    def forward(self, h, ctx):
+        z = linear(plain(h), self.up)
+        kernels.activation(z, z, self.activation)
+        return linear(z, self.down, out_dtype=torch.float32)
