@@ -256,13 +256,36 @@ def latent_configs(size: dict, vocab: int = 32768):
     return satedra, qwen
 
 
-DESIGNS = {"niduvik": ("Niduvik", "Qwen3 of equal width, heads, feed-forward and depth", hybrid_configs),
-           "satedra": ("Satedra", "Qwen3 of equal width, heads and depth, its feed-forward as wide as the experts a token passes", latent_configs)}
+def parallel_configs(size: dict, vocab: int = 32768):
+    """Nubipel at these layer sizes (a delta-rule layer, a chunked attention, a latent attention, a delta-rule layer, and so
+    on): attention heads of 128 in chunks of 1,024 positions with sinks; latent attention with heads of 64, a latent of 256
+    for keys and values and one of width / 4 for the queries; the delta rule with width / 128 heads of 128 value elements,
+    a quarter as many query/key heads of 128, 4 taps; every layer with the dense feed-forward beside its mixer.  Beside it
+    Niduvik, the engine's other model of attention layers with a bounded sight next to recurrent layers, at equal width,
+    heads, feed-forward and depth."""
+    w = size["width"]
+    mlp = {"kind": "dense", "ff": size["ff"]}
+    attention = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024}}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": size["heads"], "dim": 64, "vdim": 64, "kv_rank": 256, "q_rank": w // 4, "scale": 64 ** -0.5}}
+    delta = {"type": "delta", "mlp": mlp, "mixer": {"heads": w // 128, "kv_heads": max(w // 512, 1), "dim": 128, "vdim": 128, "conv": 4}}
+    layers = [(delta, attention, latent, delta)[i % 4] for i in range(size["layers"])]
+    nubipel = {"architecture": "Nubipel", "vocab": vocab, "width": w, "norm": {"eps": 1e-6}, "embedding": {"scale": w ** 0.5},
+               "logit_scale": w ** -0.5, "logit_softcap": 30.0, "layers": layers}
+    return nubipel, hybrid_configs(size, vocab)[0]
+
+
+# design: (title, what stands beside it, the key of that model in the output, the two configurations)
+DESIGNS = {"niduvik": ("Niduvik", "Qwen3 of equal width, heads, feed-forward and depth", "qwen3", hybrid_configs),
+           "satedra": ("Satedra", "Qwen3 of equal width, heads and depth, its feed-forward as wide as the experts a token passes", "qwen3",
+                       latent_configs),
+           "nubipel": ("Nubipel", "Niduvik of equal width, heads, feed-forward and depth", "niduvik", parallel_configs)}
 
 
 def hybrid_run(args, torch, peak: dict) -> dict:
     """`--design NAME`: prefill of one prompt and decode steps of the design at layer sizes of real models, beside the
-    Qwen3 of equal sizes, both with seeded random weights in bfloat16, timed on the device; with --kernel-shares each
+    engine's closest other model at equal sizes, both with seeded random weights in bfloat16, timed on the device; with --kernel-shares each
     model's kernels by their share of the device's time (standard error)."""
     from mini_rsglang_b200 import RuntimeConfig, kernels
     from mini_rsglang_b200.engine import EngineHandle, SequenceStep
@@ -270,12 +293,12 @@ def hybrid_run(args, torch, peak: dict) -> dict:
 
     size = HYBRID_SIZES[args.size]
     context, batch, prompt_len = args.context, args.batch, args.prompt
-    title, beside, configs = DESIGNS[args.design]
+    title, beside, beside_key, configs = DESIGNS[args.design]
     out = {"design": title, "beside": beside, "size": dict(size, name=args.size),
            "batch": batch, "context": context, "prompt": prompt_len, "dtype": "bf16", "data": "synthetic: seeded random weights",
            "peaks": peak}
     gen = torch.Generator().manual_seed(7)
-    for name, raw in zip((args.design, "qwen3"), configs(size)):
+    for name, raw in zip((args.design, beside_key), configs(size)):
         config = config_from_dict(raw)
         page = 16
         pages = batch * (-(-context // page)) + 2 * (-(-prompt_len // page)) + 8
@@ -364,7 +387,7 @@ def main() -> int:
     parser.add_argument("--output-tokens", type=int, default=64, help="--continuous: generated tokens a request")
     parser.add_argument("--prefill-budget", type=int, default=512, help="--continuous: tokens a step")
     parser.add_argument("--max-running", type=int, default=64, help="--continuous: requests in flight at most")
-    parser.add_argument("--design", choices=sorted(DESIGNS), help="that design beside the Qwen3 of equal sizes (prefill and decode), instead of the default measurement")
+    parser.add_argument("--design", choices=sorted(DESIGNS), help="that design beside the engine's closest other model at equal sizes (prefill and decode), instead of the default measurement")
     parser.add_argument("--size", choices=sorted(HYBRID_SIZES), default="1b", help="--design: layer sizes")
     parser.add_argument("--prompt", type=int, default=2048, help="--design: tokens of the prompt")
     parser.add_argument("--kernel-shares", action="store_true",

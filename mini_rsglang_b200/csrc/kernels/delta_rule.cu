@@ -13,7 +13,8 @@
 // facts come from device arrays only, so a step can be recorded.
 //
 //   delta_prepare     per token: q and k of every group to unit length in place; beta and g of every head
-//   delta_scan        the recurrence token by token; one block a (sequence, head, slice of S's columns)
+//   delta_scan        the recurrence token by token; one block a (sequence, head, slice of S's columns), the tokens'
+//                     inputs staged through shared memory ahead of their use
 //   head_norm_gate    o / rms(o) * weight * silu(gate) per (token, head)
 #include "common.cuh"
 
@@ -46,21 +47,39 @@ __global__ void delta_prepare_kernel(float* __restrict__ qkv, int qkv_width, con
     }
 }
 
+__device__ __forceinline__ uint32_t shared_address(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void copy_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(shared_address(dst)), "l"(src));
+}
+__device__ __forceinline__ void copy_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(shared_address(dst)), "l"(src));
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 // Thread (column c of the block's slice, part p): rows p * PER .. p * PER + PER - 1 of column c of S in registers; the
-// lanes of one column are neighbours, so that the two sums over d are a few shuffles.  The next token's inputs are
-// asked for before this token's arithmetic.
+// lanes of one column are neighbours, so that the two sums over d are a few shuffles.  The tokens' inputs (k and q of the
+// head's group, the slice of v, beta and g) come in batches of `batch_tokens` through two stages of shared memory: the
+// next batch is copied while this one is computed, and the threads of a block share what they read.  A token in shared
+// memory: k [parts * PER] | q [parts * PER] | v [cols rounded up to 4] | beta, g, 0, 0; the rows beyond d stay zero.
 template <int PER>
 __global__ void delta_scan_kernel(const float* __restrict__ qkv, int qkv_width, const float* __restrict__ coef,
                                   float* __restrict__ state, long long state_stride, const int* __restrict__ positions,
                                   const int* __restrict__ q_start, const int* __restrict__ state_slots, float* __restrict__ out,
-                                  int heads, int groups, int d, int e, int parts, int cols, int write_state) {
+                                  int heads, int groups, int d, int e, int parts, int cols, int batch_tokens, int wide_copies,
+                                  int write_state) {
+    extern __shared__ __align__(16) float stage[];
     pdl_launch_dependents();
+    const int rows_pad = parts * PER, cols_pad = (cols + 3) & ~3;
+    const int token_floats = 2 * rows_pad + cols_pad + 4, stage_floats = batch_tokens * token_floats;
+    for (int i = threadIdx.x; i < 2 * stage_floats; i += blockDim.x) stage[i] = 0.0f;
+    __syncthreads();
     pdl_wait();
     const int seq = blockIdx.x, head = blockIdx.y;
     const int first = q_start[seq], last = q_start[seq + 1];
     const int slot = state_slots[seq];
     if (slot < 0 || last <= first) return;
-    const int part = threadIdx.x % parts, col = blockIdx.z * cols + threadIdx.x / parts;
+    const int part = threadIdx.x % parts, col_in_slice = threadIdx.x / parts, col = blockIdx.z * cols + col_in_slice;
     const bool live = col < e;                       // a slice may overhang the head; its threads still take part in the shuffles
     const int c = live ? col : 0;
     const int group = head / (heads / groups);
@@ -71,39 +90,69 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int qkv_width, 
 #pragma unroll
     for (int i = 0; i < PER; ++i) s[i] = (!fresh && live && row0 + i < d) ? mine[(size_t)(row0 + i) * e] : 0.0f;
 
-    const size_t q_at = (size_t)group * d + row0, k_at = (size_t)(groups + group) * d + row0, v_at = (size_t)2 * groups * d + (size_t)head * e + c;
-    float kq[2][2][PER], v[2], beta[2], decay[2];
-    auto fetch = [&](int t, int b) {
-        const float* row = qkv + (size_t)t * qkv_width;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            kq[b][0][i] = row0 + i < d ? row[k_at + i] : 0.0f;
-            kq[b][1][i] = row0 + i < d ? row[q_at + i] : 0.0f;
+    const size_t q_at = (size_t)group * d, k_at = (size_t)(groups + group) * d, v_at = (size_t)2 * groups * d + (size_t)head * e + (size_t)blockIdx.z * cols;
+    const int live_cols = min(cols, e - (int)blockIdx.z * cols);
+    auto issue = [&](int t0, int n, int buffer) {
+        float* base = stage + buffer * stage_floats;
+        const int width = wide_copies ? d >> 2 : d;              // copies a vector of d elements: 16 bytes or 4 bytes each
+        for (int i = threadIdx.x; i < n * 2 * width; i += blockDim.x) {
+            const int j = i / (2 * width), r = i % (2 * width), which = r / width, at = r % width;
+            const float* src = qkv + (size_t)(t0 + j) * qkv_width + (which ? q_at : k_at);
+            float* dst = base + j * token_floats + which * rows_pad;
+            if (wide_copies) copy_async16(dst + at * 4, src + at * 4);
+            else copy_async4(dst + at, src + at);
         }
-        v[b] = row[v_at];
-        beta[b] = coef[(size_t)t * 2 * heads + head];
-        decay[b] = coef[(size_t)t * 2 * heads + heads + head];
+        for (int i = threadIdx.x; i < n * (live_cols + 2); i += blockDim.x) {
+            const int j = i / (live_cols + 2), r = i % (live_cols + 2);
+            float* dst = base + j * token_floats + 2 * rows_pad;
+            if (r < live_cols) copy_async4(dst + r, qkv + (size_t)(t0 + j) * qkv_width + v_at + r);
+            else copy_async4(dst + cols_pad + (r - live_cols), coef + (size_t)(t0 + j) * 2 * heads + (r == live_cols ? head : heads + head));
+        }
+        copy_async_commit();
     };
-    fetch(first, 0);
-    for (int t = first; t < last; ++t) {
-        const int b = (t - first) & 1;
-        if (t + 1 < last) fetch(t + 1, b ^ 1);
-        float r = 0.0f;
-#pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            s[i] *= decay[b];
-            r += s[i] * kq[b][0][i];
+    const int batches = (last - first + batch_tokens - 1) / batch_tokens;
+    issue(first, min(batch_tokens, last - first), 0);
+    for (int b = 0; b < batches; ++b) {
+        const int t0 = first + b * batch_tokens, n = min(batch_tokens, last - t0);
+        if (b + 1 < batches) {
+            issue(t0 + batch_tokens, min(batch_tokens, last - t0 - batch_tokens), (b + 1) & 1);
+            copy_async_wait<1>();
+        } else {
+            copy_async_wait<0>();
         }
-        for (int o = parts >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-        const float u = beta[b] * (v[b] - r);
-        float y = 0.0f;
+        __syncthreads();
+        const float* base = stage + (b & 1) * stage_floats;
+        for (int j = 0; j < n; ++j) {
+            const float* token = base + j * token_floats;
+            float k[PER], q[PER];
 #pragma unroll
-        for (int i = 0; i < PER; ++i) {
-            s[i] += kq[b][0][i] * u;
-            y += s[i] * kq[b][1][i];
+            for (int i = 0; i < PER; i += 4) {
+                const float4 kk = *reinterpret_cast<const float4*>(token + row0 + i);
+                const float4 qq = *reinterpret_cast<const float4*>(token + rows_pad + row0 + i);
+                k[i] = kk.x, k[i + 1] = kk.y, k[i + 2] = kk.z, k[i + 3] = kk.w;
+                q[i] = qq.x, q[i + 1] = qq.y, q[i + 2] = qq.z, q[i + 3] = qq.w;
+            }
+            const float v = token[2 * rows_pad + col_in_slice], beta = token[2 * rows_pad + cols_pad], decay = token[2 * rows_pad + cols_pad + 1];
+            float r4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                s[i] *= decay;
+                r4[i & 3] += s[i] * k[i];
+            }
+            float r = (r4[0] + r4[1]) + (r4[2] + r4[3]);
+            for (int o = parts >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+            const float u = beta * (v - r);
+            float y4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                s[i] += k[i] * u;
+                y4[i & 3] += s[i] * q[i];
+            }
+            float y = (y4[0] + y4[1]) + (y4[2] + y4[3]);
+            for (int o = parts >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (live && part == 0) out[(size_t)(t0 + j) * heads * e + (size_t)head * e + c] = y;
         }
-        for (int o = parts >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-        if (live && part == 0) out[(size_t)t * heads * e + (size_t)head * e + c] = y;
+        __syncthreads();                                  // the stage is copied into again two batches on
     }
     if (write_state && live) {
 #pragma unroll
@@ -156,14 +205,23 @@ MRS_EXPORT int mrs_delta_scan(const float* qkv, const float* coef, float* state,
     constexpr int PER = 16;
     int parts = 1;
     while (parts * PER < d) parts <<= 1;                 // lanes a column: a power of two, at most 32
-    // columns a block: as few as still give every multiprocessor two blocks, at least a warp's worth of threads
+    // columns a block: four warps' worth of threads (they share the tokens' keys and queries in shared memory), fewer while
+    // the blocks would leave half the multiprocessors idle, at least a warp's worth of threads
     int cols = 128 / parts;
+    while (cols > e && cols * parts > 32) cols >>= 1;
     const long long pairs = (long long)sequences * heads;
-    while (cols * parts > 32 && pairs * ((e + cols - 1) / cols) < 2LL * mrs_sm_count()) cols >>= 1;
+    while (cols * parts > 32 && pairs * ((e + cols - 1) / cols) * 2 < mrs_sm_count()) cols >>= 1;
     const int slices = (e + cols - 1) / cols;
     if (slices > 65535) return MRS_BAD_ARGUMENT;
-    MRS_LAUNCH(delta_scan_kernel<PER>, dim3(sequences, heads, slices), cols * parts, 0, stream, qkv, 2 * groups * d + heads * e, coef,
-               state, state_stride, positions, q_start, state_slots, out, heads, groups, d, e, parts, cols, write_state);
+    const int qkv_width = 2 * groups * d + heads * e;
+    const int token_floats = 2 * parts * PER + ((cols + 3) & ~3) + 4;
+    int batch_tokens = (48 * 1024) / (2 * token_floats * (int)sizeof(float));
+    if (batch_tokens > 8) batch_tokens = 8;
+    if (batch_tokens < 1) return MRS_BAD_ARGUMENT;
+    const int wide_copies = d % 4 == 0 && qkv_width % 4 == 0 && ((uintptr_t)qkv & 15) == 0;
+    MRS_LAUNCH(delta_scan_kernel<PER>, dim3(sequences, heads, slices), cols * parts, 2 * batch_tokens * token_floats * sizeof(float), stream,
+               qkv, qkv_width, coef, state, state_stride, positions, q_start, state_slots, out, heads, groups, d, e, parts, cols,
+               batch_tokens, wide_copies, write_state);
     MRS_RETURN_LAUNCH_STATUS();
 }
 
