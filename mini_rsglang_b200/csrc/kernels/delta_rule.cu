@@ -58,20 +58,33 @@ __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.com
 template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
 // Thread (column c of the block's slice, part p): rows p * PER .. p * PER + PER - 1 of column c of S in registers; the
-// lanes of one column are neighbours, so that the two sums over d are a few shuffles.  The tokens' inputs (k and q of the
-// head's group, the slice of v, beta and g) come in batches of `batch_tokens` through two stages of shared memory: the
-// next batch is copied while this one is computed, and the threads of a block share what they read.  A token in shared
-// memory: k [parts * PER] | q [parts * PER] | v [cols rounded up to 4] | beta, g, 0, 0; the rows beyond d stay zero.
-template <int PER>
-__global__ void delta_scan_kernel(const float* __restrict__ qkv, int qkv_width, const float* __restrict__ coef,
+// PARTS lanes of one column are neighbours, so that the two sums over d are log2(PARTS) shuffles.  The tokens' inputs (k and
+// q of the head's group, the slice of v, beta and g) come in batches of `batch_tokens` through two stages of shared memory:
+// the next batch is copied while this one is computed, and the threads of a block share what they read.  A token in shared
+// memory: k [PARTS * PITCH] | q [PARTS * PITCH] | v [cols rounded up to 4] | beta, g, 0, 0, with PITCH = PER + 4, so that
+// the 16-byte reads of the parts fall on different banks; the rows beyond d stay zero.
+//
+// One warp a scheduler is all that a single sequence offers, so every instruction's latency shows.  What a thread copies is
+// therefore the same in every batch and worked out once, ahead of the loop (`Copies`); and the chain from token to token is
+// only: the sum over S's old rows times k, the shuffles, u, one fused multiply-add a row.  The decay is applied to S beside
+// the shuffles (r = g * sum(S_old k)), and the read-out of one token overlaps the next one's chain.
+template <int N>
+struct Copies {
+    int src[N], dst[N], token[N];      // offsets in floats from the batch's first row and from the stage; a huge token: none
+};
+
+template <int PER, int PARTS>
+__global__ void __launch_bounds__(128) delta_scan_kernel(const float* __restrict__ qkv, int qkv_width, const float* __restrict__ coef,
                                   float* __restrict__ state, long long state_stride, const int* __restrict__ positions,
                                   const int* __restrict__ q_start, const int* __restrict__ state_slots, float* __restrict__ out,
-                                  int heads, int groups, int d, int e, int parts, int cols, int batch_tokens, int wide_copies,
+                                  int heads, int groups, int d, int e, int cols, int batch_tokens, int wide_copies,
                                   int write_state) {
     extern __shared__ __align__(16) float stage[];
+    constexpr int PITCH = PER + 4, ROWS = PARTS * PITCH;
+    constexpr int WIDE = 8, NARROW = 3;                    // copies a thread and batch that are worked out ahead
     pdl_launch_dependents();
-    const int rows_pad = parts * PER, cols_pad = (cols + 3) & ~3;
-    const int token_floats = 2 * rows_pad + cols_pad + 4, stage_floats = batch_tokens * token_floats;
+    const int cols_pad = (cols + 3) & ~3;
+    const int token_floats = 2 * ROWS + cols_pad + 4, stage_floats = batch_tokens * token_floats;
     for (int i = threadIdx.x; i < 2 * stage_floats; i += blockDim.x) stage[i] = 0.0f;
     __syncthreads();
     pdl_wait();
@@ -79,7 +92,7 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int qkv_width, 
     const int first = q_start[seq], last = q_start[seq + 1];
     const int slot = state_slots[seq];
     if (slot < 0 || last <= first) return;
-    const int part = threadIdx.x % parts, col_in_slice = threadIdx.x / parts, col = blockIdx.z * cols + col_in_slice;
+    const int part = threadIdx.x % PARTS, col_in_slice = threadIdx.x / PARTS, col = blockIdx.z * cols + col_in_slice;
     const bool live = col < e;                       // a slice may overhang the head; its threads still take part in the shuffles
     const int c = live ? col : 0;
     const int group = head / (heads / groups);
@@ -90,27 +103,75 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int qkv_width, 
 #pragma unroll
     for (int i = 0; i < PER; ++i) s[i] = (!fresh && live && row0 + i < d) ? mine[(size_t)(row0 + i) * e] : 0.0f;
 
-    const size_t q_at = (size_t)group * d, k_at = (size_t)(groups + group) * d, v_at = (size_t)2 * groups * d + (size_t)head * e + (size_t)blockIdx.z * cols;
+    const int q_at = group * d, k_at = (groups + group) * d, v_at = 2 * groups * d + head * e + (int)blockIdx.z * cols;
     const int live_cols = min(cols, e - (int)blockIdx.z * cols);
+    // copy number i of a batch's keys and queries: token j, k or q, elements el .. of the vector
+    const int width = wide_copies ? d >> 2 : d, vector_copies = batch_tokens * 2 * width;
+    auto vector_copy = [&](int i, int& src, int& dst) {
+        const int j = i / (2 * width), r = i % (2 * width), which = r / width, el = (r % width) * (wide_copies ? 4 : 1);
+        src = j * qkv_width + (which ? q_at : k_at) + el;
+        dst = j * token_floats + which * ROWS + (el / PER) * PITCH + el % PER;
+        return j;
+    };
+    // copy number i of a batch's values and coefficients: token j, a column of v, beta or g
+    const int scalar_copies = batch_tokens * (live_cols + 2);
+    auto scalar_copy = [&](int i, long long& src, int& dst) {
+        const int j = i / (live_cols + 2), r = i % (live_cols + 2);
+        if (r < live_cols) {
+            src = (long long)j * qkv_width + v_at + r;
+            dst = j * token_floats + 2 * ROWS + r;
+        } else {
+            src = -1 - ((long long)j * 2 * heads + (r == live_cols ? head : heads + head));      // below zero: from coef
+            dst = j * token_floats + 2 * ROWS + cols_pad + (r - live_cols);
+        }
+        return j;
+    };
+    Copies<WIDE> wide;
+    Copies<NARROW> narrow;
+    long long narrow_src[NARROW];
+    const int longest = min(batch_tokens, last - first);       // a decoded token alone needs the first token's copies only
+#pragma unroll
+    for (int i = 0; i < WIDE; ++i) {
+        const int at = threadIdx.x + i * blockDim.x;
+        wide.token[i] = at < longest * 2 * width ? vector_copy(at, wide.src[i], wide.dst[i]) : (1 << 30);
+    }
+#pragma unroll
+    for (int i = 0; i < NARROW; ++i) {
+        const int at = threadIdx.x + i * blockDim.x;
+        narrow.token[i] = at < longest * (live_cols + 2) ? scalar_copy(at, narrow_src[i], narrow.dst[i]) : (1 << 30);
+    }
     auto issue = [&](int t0, int n, int buffer) {
         float* base = stage + buffer * stage_floats;
-        const int width = wide_copies ? d >> 2 : d;              // copies a vector of d elements: 16 bytes or 4 bytes each
-        for (int i = threadIdx.x; i < n * 2 * width; i += blockDim.x) {
-            const int j = i / (2 * width), r = i % (2 * width), which = r / width, at = r % width;
-            const float* src = qkv + (size_t)(t0 + j) * qkv_width + (which ? q_at : k_at);
-            float* dst = base + j * token_floats + which * rows_pad;
-            if (wide_copies) copy_async16(dst + at * 4, src + at * 4);
-            else copy_async4(dst + at, src + at);
+        const float* rows = qkv + (size_t)t0 * qkv_width;
+        const float* facts = coef + (size_t)t0 * 2 * heads;
+#pragma unroll
+        for (int i = 0; i < WIDE; ++i)
+            if (wide.token[i] < n) {
+                if (wide_copies) copy_async16(base + wide.dst[i], rows + wide.src[i]);
+                else copy_async4(base + wide.dst[i], rows + wide.src[i]);
+            }
+        for (int at = threadIdx.x + WIDE * blockDim.x; at < vector_copies; at += blockDim.x) {      // sizes beyond the usual
+            int src, dst;
+            if (vector_copy(at, src, dst) < n) {
+                if (wide_copies) copy_async16(base + dst, rows + src);
+                else copy_async4(base + dst, rows + src);
+            }
         }
-        for (int i = threadIdx.x; i < n * (live_cols + 2); i += blockDim.x) {
-            const int j = i / (live_cols + 2), r = i % (live_cols + 2);
-            float* dst = base + j * token_floats + 2 * rows_pad;
-            if (r < live_cols) copy_async4(dst + r, qkv + (size_t)(t0 + j) * qkv_width + v_at + r);
-            else copy_async4(dst + cols_pad + (r - live_cols), coef + (size_t)(t0 + j) * 2 * heads + (r == live_cols ? head : heads + head));
+#pragma unroll
+        for (int i = 0; i < NARROW; ++i)
+            if (narrow.token[i] < n) copy_async4(base + narrow.dst[i], narrow_src[i] >= 0 ? rows + narrow_src[i] : facts + (-1 - narrow_src[i]));
+        for (int at = threadIdx.x + NARROW * blockDim.x; at < scalar_copies; at += blockDim.x) {
+            long long src;
+            int dst;
+            if (scalar_copy(at, src, dst) < n) copy_async4(base + dst, src >= 0 ? rows + src : facts + (-1 - src));
         }
         copy_async_commit();
     };
     const int batches = (last - first + batch_tokens - 1) / batch_tokens;
+    const int token_tail = 2 * ROWS + cols_pad;
+    float* out_at = out + (size_t)first * heads * e + (size_t)head * e + c;
+    const size_t out_step = (size_t)heads * e;
+    const bool writes = live && part == 0;
     issue(first, min(batch_tokens, last - first), 0);
     for (int b = 0; b < batches; ++b) {
         const int t0 = first + b * batch_tokens, n = min(batch_tokens, last - t0);
@@ -121,36 +182,38 @@ __global__ void delta_scan_kernel(const float* __restrict__ qkv, int qkv_width, 
             copy_async_wait<0>();
         }
         __syncthreads();
-        const float* base = stage + (b & 1) * stage_floats;
-        for (int j = 0; j < n; ++j) {
-            const float* token = base + j * token_floats;
+        const float* token = stage + (b & 1) * stage_floats + part * PITCH;
+#pragma unroll 2
+        for (int j = 0; j < n; ++j, token += token_floats, out_at += out_step) {
             float k[PER], q[PER];
 #pragma unroll
             for (int i = 0; i < PER; i += 4) {
-                const float4 kk = *reinterpret_cast<const float4*>(token + row0 + i);
-                const float4 qq = *reinterpret_cast<const float4*>(token + rows_pad + row0 + i);
+                const float4 kk = *reinterpret_cast<const float4*>(token + i);
+                const float4 qq = *reinterpret_cast<const float4*>(token + ROWS + i);
                 k[i] = kk.x, k[i + 1] = kk.y, k[i + 2] = kk.z, k[i + 3] = kk.w;
                 q[i] = qq.x, q[i + 1] = qq.y, q[i + 2] = qq.z, q[i + 3] = qq.w;
             }
-            const float v = token[2 * rows_pad + col_in_slice], beta = token[2 * rows_pad + cols_pad], decay = token[2 * rows_pad + cols_pad + 1];
+            const float* tail = token - part * PITCH + token_tail;
+            const float v = (tail - cols_pad)[col_in_slice], beta = tail[0], decay = tail[1];
             float r4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                s[i] *= decay;
-                r4[i & 3] += s[i] * k[i];
-            }
+            for (int i = 0; i < PER; ++i) r4[i & 3] = fmaf(s[i], k[i], r4[i & 3]);
             float r = (r4[0] + r4[1]) + (r4[2] + r4[3]);
-            for (int o = parts >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-            const float u = beta * (v - r);
+#pragma unroll
+            for (int o = PARTS >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) s[i] *= decay;                 // beside the shuffles, off the chain
+            const float u = beta * (v - decay * r);
             float y4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int i = 0; i < PER; ++i) {
-                s[i] += k[i] * u;
-                y4[i & 3] += s[i] * q[i];
+                s[i] = fmaf(k[i], u, s[i]);
+                y4[i & 3] = fmaf(s[i], q[i], y4[i & 3]);
             }
             float y = (y4[0] + y4[1]) + (y4[2] + y4[3]);
-            for (int o = parts >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (live && part == 0) out[(size_t)(t0 + j) * heads * e + (size_t)head * e + c] = y;
+#pragma unroll
+            for (int o = PARTS >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+            if (writes) *out_at = y;
         }
         __syncthreads();                                  // the stage is copied into again two batches on
     }
@@ -214,14 +277,25 @@ MRS_EXPORT int mrs_delta_scan(const float* qkv, const float* coef, float* state,
     const int slices = (e + cols - 1) / cols;
     if (slices > 65535) return MRS_BAD_ARGUMENT;
     const int qkv_width = 2 * groups * d + heads * e;
-    const int token_floats = 2 * parts * PER + ((cols + 3) & ~3) + 4;
+    const int token_floats = 2 * parts * (PER + 4) + ((cols + 3) & ~3) + 4;
     int batch_tokens = (48 * 1024) / (2 * token_floats * (int)sizeof(float));
     if (batch_tokens > 8) batch_tokens = 8;
     if (batch_tokens < 1) return MRS_BAD_ARGUMENT;
     const int wide_copies = d % 4 == 0 && qkv_width % 4 == 0 && ((uintptr_t)qkv & 15) == 0;
-    MRS_LAUNCH(delta_scan_kernel<PER>, dim3(sequences, heads, slices), cols * parts, 2 * batch_tokens * token_floats * sizeof(float), stream,
-               qkv, qkv_width, coef, state, state_stride, positions, q_start, state_slots, out, heads, groups, d, e, parts, cols,
-               batch_tokens, wide_copies, write_state);
+    const dim3 grid(sequences, heads, slices);
+    const size_t shared = 2 * (size_t)batch_tokens * token_floats * sizeof(float);
+#define MRS_DELTA_SCAN(PARTS)                                                                                                        \
+    MRS_LAUNCH((delta_scan_kernel<PER, PARTS>), grid, cols * PARTS, shared, stream, qkv, qkv_width, coef, state, state_stride,       \
+               positions, q_start, state_slots, out, heads, groups, d, e, cols, batch_tokens, wide_copies, write_state)
+    switch (parts) {
+        case 1: MRS_DELTA_SCAN(1); break;
+        case 2: MRS_DELTA_SCAN(2); break;
+        case 4: MRS_DELTA_SCAN(4); break;
+        case 8: MRS_DELTA_SCAN(8); break;
+        case 16: MRS_DELTA_SCAN(16); break;
+        default: MRS_DELTA_SCAN(32); break;
+    }
+#undef MRS_DELTA_SCAN
     MRS_RETURN_LAUNCH_STATUS();
 }
 
