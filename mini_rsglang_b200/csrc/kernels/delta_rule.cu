@@ -57,7 +57,8 @@ __device__ __forceinline__ void copy_async4(void* dst, const void* src) {
 __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-// Thread (column c of the block's slice, part p): rows p * PER .. p * PER + PER - 1 of column c of S in registers; the
+// Thread (column c of the block's slice, part p): rows p * PER .. p * PER + PER - 1 of column c of S in registers (PER is
+// 16 or 8, the launcher's choice); the
 // PARTS lanes of one column are neighbours, so that the two sums over d are log2(PARTS) shuffles.  The tokens' inputs (k and
 // q of the head's group, the slice of v, beta and g) come in batches of `batch_tokens` through two stages of shared memory:
 // the next batch is copied while this one is computed, and the threads of a block share what they read.  A token in shared
@@ -265,36 +266,46 @@ MRS_EXPORT int mrs_delta_scan(const float* qkv, const float* coef, float* state,
                               int groups, int d, int e, int write_state, void* stream) {
     if (tokens <= 0 || sequences <= 0) return 0;
     if (groups <= 0 || d <= 0 || d > 512 || heads <= 0 || e <= 0 || heads % groups || heads > 65535) return MRS_BAD_ARGUMENT;
-    constexpr int PER = 16;
-    int parts = 1;
-    while (parts * PER < d) parts <<= 1;                 // lanes a column: a power of two, at most 32
-    // columns a block: four warps' worth of threads (they share the tokens' keys and queries in shared memory), fewer while
-    // the blocks would leave half the multiprocessors idle, at least a warp's worth of threads
-    int cols = 128 / parts;
-    while (cols > e && cols * parts > 32) cols >>= 1;
     const long long pairs = (long long)sequences * heads;
-    while (cols * parts > 32 && pairs * ((e + cols - 1) / cols) * 2 < mrs_sm_count()) cols >>= 1;
-    const int slices = (e + cols - 1) / cols;
+    int per, parts, cols, slices;
+    auto plan = [&](int rows) {
+        per = rows;
+        parts = 1;
+        while (parts * per < d) parts <<= 1;             // lanes a column: a power of two, at most 32
+        // columns a block: four warps' worth of threads (they share the tokens' keys and queries in shared memory), fewer
+        // while the blocks would leave half the multiprocessors idle, at least a warp's worth of threads
+        cols = 128 / parts;
+        while (cols > e && cols * parts > 32) cols >>= 1;
+        while (cols * parts > 32 && pairs * ((e + cols - 1) / cols) * 2 < mrs_sm_count()) cols >>= 1;
+        slices = (e + cols - 1) / cols;
+    };
+    // rows of a column a thread: 16; 8 where long portions come as more blocks than multiprocessors, so that more of them
+    // are resident side by side (measured: from 1.1 to 1.3 times as fast there, slower for short portions and few blocks)
+    plan(16);
+    if (d <= 256 && tokens >= 256LL * sequences && pairs * slices > mrs_sm_count()) plan(8);
     if (slices > 65535) return MRS_BAD_ARGUMENT;
     const int qkv_width = 2 * groups * d + heads * e;
-    const int token_floats = 2 * parts * (PER + 4) + ((cols + 3) & ~3) + 4;
+    const int token_floats = 2 * parts * (per + 4) + ((cols + 3) & ~3) + 4;
     int batch_tokens = (48 * 1024) / (2 * token_floats * (int)sizeof(float));
     if (batch_tokens > 8) batch_tokens = 8;
     if (batch_tokens < 1) return MRS_BAD_ARGUMENT;
     const int wide_copies = d % 4 == 0 && qkv_width % 4 == 0 && ((uintptr_t)qkv & 15) == 0;
     const dim3 grid(sequences, heads, slices);
     const size_t shared = 2 * (size_t)batch_tokens * token_floats * sizeof(float);
-#define MRS_DELTA_SCAN(PARTS)                                                                                                        \
+#define MRS_DELTA_SCAN(PER, PARTS)                                                                                                   \
     MRS_LAUNCH((delta_scan_kernel<PER, PARTS>), grid, cols * PARTS, shared, stream, qkv, qkv_width, coef, state, state_stride,       \
                positions, q_start, state_slots, out, heads, groups, d, e, cols, batch_tokens, wide_copies, write_state)
-    switch (parts) {
-        case 1: MRS_DELTA_SCAN(1); break;
-        case 2: MRS_DELTA_SCAN(2); break;
-        case 4: MRS_DELTA_SCAN(4); break;
-        case 8: MRS_DELTA_SCAN(8); break;
-        case 16: MRS_DELTA_SCAN(16); break;
-        default: MRS_DELTA_SCAN(32); break;
+#define MRS_DELTA_SCAN_ROWS(PER)                                                                                                     \
+    switch (parts) {                                                                                                                 \
+        case 1: MRS_DELTA_SCAN(PER, 1); break;                                                                                       \
+        case 2: MRS_DELTA_SCAN(PER, 2); break;                                                                                       \
+        case 4: MRS_DELTA_SCAN(PER, 4); break;                                                                                       \
+        case 8: MRS_DELTA_SCAN(PER, 8); break;                                                                                       \
+        case 16: MRS_DELTA_SCAN(PER, 16); break;                                                                                     \
+        default: MRS_DELTA_SCAN(PER, 32); break;                                                                                     \
     }
+    if (per == 16) { MRS_DELTA_SCAN_ROWS(16) } else { MRS_DELTA_SCAN_ROWS(8) }
+#undef MRS_DELTA_SCAN_ROWS
 #undef MRS_DELTA_SCAN
     MRS_RETURN_LAUNCH_STATUS();
 }

@@ -532,6 +532,28 @@ def test_delta_rule_kernels_in_portions_with_slots_used_again(H, G, d, e, taps):
     assert (out16.double().cpu() - want[0][:9]).abs().max() < 8e-3 * max(1.0, want[0][:9].abs().max().item())
 
 
+def test_delta_rule_long_portions_of_many_heads():
+    """A long portion of many heads comes as more blocks than the GPU has multiprocessors and takes the recurrence kernel
+    with fewer rows of S a thread; the short portion after it takes the usual one from the state that the long one left."""
+    H, G, d, e, taps = 40, 8, 128, 64, 2
+    length, cuts = 269, [262, 7]
+    channels = 2 * G * d + H * e
+    proj, w = delta_inputs(length, H, G, d, e, taps, 91)
+    dev = {k: t.to(DEV).contiguous() for k, t in w.items()}
+    want = plain_delta(proj, w, H, G, d, e, 1e-5)
+    state = torch.full((2, (taps - 1) * channels + H * d * e), -7.0, device=DEV)
+    got, done = torch.zeros(length, H * e, dtype=torch.float64), 0
+    for n in cuts:
+        rows = proj[done:done + n].to(DEV).contiguous()
+        out = run_delta(rows, dev, state, H, G, d, e, taps, torch.arange(done, done + n, dtype=torch.int32, device=DEV),
+                        torch.zeros(n, dtype=torch.int32, device=DEV), torch.tensor([0, n], dtype=torch.int32, device=DEV),
+                        torch.tensor([1], dtype=torch.int32, device=DEV), 1e-5)
+        got[done:done + n] = out.double().cpu()
+        done += n
+    assert (got - want).abs().max() < 2e-4 * max(1.0, want.abs().max().item())
+    assert (state[0] == -7.0).all()
+
+
 def test_delta_rule_keeps_a_far_token_and_corrects_it():
     """A head that hardly forgets carries one early token's value over hundreds of single-token steps in its float32 state;
     a later token with the same key and beta 1 replaces it, and the very last token reads the replacement."""
