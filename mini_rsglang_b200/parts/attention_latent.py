@@ -168,6 +168,19 @@ class LatentAttention(Mixer):
                                           self.scale, window=self.window, gate=gate)
         else:
             narrow, wide, longest, _ = plan_attention_tiles(ctx, *arguments)
+            few = kernels.MMA_ROWS_NARROW
+            if ctx.decode_tiles is not None and narrow is None and H > few and H % few == 0:
+                # single tokens of more heads than a tile of few rows holds: all heads read the same cache rows, so any
+                # `few` of them are as good a group as all; a token becomes H / few rows of that many heads at its position,
+                # each a narrow tile whose keys CTAs share (a wide tile would walk a request's keys alone)
+                m = H // few
+                tiles, positions = self._rows_of_few_heads(ctx, m)
+                reach = min(longest, self.window) if self.window else longest
+                splits = min(choose_splits(tiles.shape[0], 1, reach, arguments[5]), 16)
+                kernels.attention_biased_mma(q_rows.view(tokens * m, few * row), cache.k, None, positions, table, tiles,
+                                             mixed.view(tokens * m, few * R), few, 1, row, R, self.scale, window=self.window,
+                                             gate=gate.view(tokens * m, few) if gate is not None else None, narrow=True, splits=splits)
+                wide = None
             for tiles, is_narrow in ((narrow, True), (wide, False)):
                 if tiles is not None:
                     splits = 1
@@ -186,6 +199,21 @@ class LatentAttention(Mixer):
                 gates = gates.repeat_interleave(self.e, dim=1)
             kernels.sigmoid_gate_mul(out, gates)
         return linear(out, self.o, out_dtype=torch.float32 if self.float32_out else None)
+
+    @staticmethod
+    def _rows_of_few_heads(ctx, m: int):
+        """A step of single tokens with every token as `m` rows: the step's tile list with tile (s, t, n, 0) as m tiles
+        (s, t * m + j, n, 0), and every token's position m times.  Made on the device from the step's own arrays (a recorded
+        step makes them anew: what its trial run made stays outside the recording); kept in the context for the other
+        layers of the same pass."""
+        made = ctx.__dict__.setdefault("_rows_of_few_heads", {})
+        key = (m, ctx.rehearsal)
+        if key not in made:
+            base = ctx.decode_tiles
+            tiles = base.repeat(1, m).view(-1, 4)
+            tiles[:, 1] = tiles[:, 1] * m + torch.arange(m, dtype=torch.int32, device=base.device).repeat(base.shape[0])
+            made[key] = (tiles, ctx.positions.view(-1, 1).expand(-1, m).contiguous().view(-1))
+        return made[key]
 
     def _tile_plan(self) -> tuple:
         """What the tile planner is asked for this attention ((): no tiles, the CUDA-core kernel takes every row).  All

@@ -74,8 +74,15 @@ SHAPE_Y = {"architecture": "Nubipel", "vocab": 97, "width": 64, "norm": {"eps": 
                dict(delta(4, 1, 64, 32, 4), mlp=None),
                dict(latent(1, 32, 48, 32, 16), mlp=dense(16)),
                dict(attention(2, 1, 128, 128, 16), mlp=None)]}
-SHAPES = {"X": (SHAPE_X, 4), "Y": (SHAPE_Y, 16)}
-LENGTHS = {"X": [70, 45, 33, 100, 130, 64, 37, 90], "Y": [1, 7, 17, 40, 129, 65, 96, 50]}
+# Z: latent attentions of more heads than a tensor-core tile of few rows holds (32 and 48: decoded tokens go as two and three
+# rows of 16 heads), and one of 24 heads (no multiple of 16: a wide tile a token).
+SHAPE_Z = {"architecture": "Nubipel", "vocab": 131, "width": 96, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+           "logit_scale": 0.5, "logit_softcap": 12.0, "layers": [
+               dict(latent(32, 16, 16, 32, 16), mlp=dense(48)),
+               dict(latent(48, 16, 32, 48, 32), mlp=None),
+               dict(latent(24, 32, 16, 64, 48), mlp=dense(32))]}
+SHAPES = {"X": (SHAPE_X, 4), "Y": (SHAPE_Y, 16), "Z": (SHAPE_Z, 16)}
+LENGTHS = {"X": [70, 45, 33, 100, 130, 64, 37, 90], "Y": [1, 7, 17, 40, 129, 65, 96, 50], "Z": [40, 75, 23, 58, 66, 31]}
 MODES = ("whole", "decode_tail", "portions", "mixed")
 
 
@@ -164,6 +171,16 @@ def test_replay_matches_plain(folders, tmp_path_factory, name, dtype, mode):
     assert rows
     for step, got, want, _ in rows:
         T.check_rows(got, want, dtype, f"{name} {dtype} {mode} step {step}")
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_latent_attention_of_many_heads(folders, tmp_path_factory, mode):
+    """Decoded tokens whose heads fill several tiles of few rows, alone and beside portions of other requests, against the
+    plain implementation."""
+    rows = replay(folders, "Z", "bfloat16", tmp_path_factory)[mode]
+    assert rows
+    for step, got, want, _ in rows:
+        T.check_rows(got, want, "bfloat16", f"Z bfloat16 {mode} step {step}")
 
 
 @pytest.mark.parametrize("name", ["X", "Y"])
