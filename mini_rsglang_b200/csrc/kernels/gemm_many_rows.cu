@@ -1,6 +1,7 @@
 // The feed-forward's first product for many rows (prompt portions) on the tcgen05 tensor cores, bfloat16 in, float32
 // accumulation, with the activation in its epilogue:
-//   out[T, N / 2] = silu(x . gate^T) * (x . up^T)
+//   out[T, N / 2] = silu(x . gate^T) * (x . up^T)          (gated feed-forwards)
+//   out[T, N]     = act(x . w^T)                            (plain ones: gelu with the error function or with tanh, silu)
 //
 // The library's product for these sizes runs near the tensor cores' peak, but it leaves its result in
 // memory, which a second kernel reads again (2,048 tokens: 150 MB and 34 us a layer).  Here a CTA computes a
@@ -10,7 +11,8 @@
 //            128-byte swizzle) into a ring of stages;
 //   warp 1   one thread issues tcgen05.mma (M 128, N 256, K 16) on the stages;
 //   warps 2-5 a thread a token: the row's 256 sums from tensor memory.  A tile holds two blocks of 64 gate
-//            and 64 up rows (the weights are stored so), so a thread has both factors of its outputs.
+//            and 64 up rows (the weights are stored so), so a thread has both factors of its outputs; the plain
+//            product applies its activation to every sum.
 // CTAs are persistent; the tiles that share a weight tile are taken by neighbouring CTAs at the same
 // time, so the weights come from HBM once.  Every wait is bounded (tma.cuh).
 //   (reference: cuBLAS and a kernel of its own, crates/models/src/qwen3.rs:255-261; ops.cu:91-94)
@@ -28,6 +30,15 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int TMEM_COLUMNS = 2 * BN;
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 16;
 
+// exact float32 forms, the same as the stand-alone activation kernel's
+__device__ __forceinline__ float activate(float z, int kind) {
+    if (kind == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+    if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    return z / (1.0f + expf(-z));
+}
+
+// ACT < 0: the gated product; 0, 1, 2: the plain product with gelu (error function), gelu (tanh) or silu on every sum.
+template <int ACT>
 __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, bf16* __restrict__ out, int T, int N, int K) {
     extern __shared__ unsigned char smem_raw[];
@@ -134,6 +145,27 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
             tcgen05_fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * BN;
             const int token = m0 + row;
+            if constexpr (ACT >= 0) {
+                bf16* dst = out + (size_t)token * N + n0;
+#pragma unroll 2
+                for (int c = 0; c < BN; c += 32) {
+                    float v[32];
+                    tmem_load_32_async(acc + c, v);
+                    tmem_load_wait();
+                    if (token < T && n0 + c < N) {                    // N is a multiple of 32
+#pragma unroll
+                        for (int e = 0; e < 32; e += 8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int p = 0; p < 4; ++p) {
+                                __nv_bfloat162 pair = __floats2bfloat162_rn(activate(v[e + 2 * p], ACT), activate(v[e + 2 * p + 1], ACT));
+                                w[p] = *reinterpret_cast<uint32_t*>(&pair);
+                            }
+                            *reinterpret_cast<uint4*>(dst + c + e) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    }
+                }
+            } else {
             bf16* dst = out + (size_t)token * half_n + (n0 >> 1);
 #pragma unroll
             for (int block = 0; block < BN / 128; ++block) {          // 64 gate columns, then their 64 up columns
@@ -159,6 +191,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
                     }
                 }
             }
+            }
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buffer]);
@@ -172,15 +205,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
     }
 }
 
+template <int ACT>
 int launch(const void* x_map, const void* w_map, void* out, int T, int N, int K, int ctas, void* stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_many_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_many_rows_kernel<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int tiles = ((T + BM - 1) / BM) * ((N + BN - 1) / BN);
-    MRS_LAUNCH(gemm_many_rows_kernel, ctas < tiles ? ctas : tiles, THREADS, SMEM_BYTES, stream, *reinterpret_cast<const CUtensorMap*>(x_map),
+    MRS_LAUNCH(gemm_many_rows_kernel<ACT>, ctas < tiles ? ctas : tiles, THREADS, SMEM_BYTES, stream, *reinterpret_cast<const CUtensorMap*>(x_map),
                *reinterpret_cast<const CUtensorMap*>(w_map), (bf16*)out, T, N, K);
     MRS_RETURN_LAUNCH_STATUS();
 }
@@ -203,7 +237,16 @@ MRS_EXPORT int mrs_gemm_many_rows_map(const void* base, long long rows, long lon
 MRS_EXPORT int mrs_gemm_gated_rows(const void* x_map, const void* w_map, void* out, int T, int N, int K, int ctas, void* stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || N % 128 || ctas < 1 || !x_map || !w_map || !out || ((uintptr_t)out & 15)) return MRS_BAD_ARGUMENT;
-    return launch(x_map, w_map, out, T, N, K, ctas, stream);
+    return launch<-1>(x_map, w_map, out, T, N, K, ctas, stream);
+}
+
+// out[T, N] = act(x . w^T) in bfloat16; act 0: gelu with the error function, 1: gelu with tanh, 2: silu.  N a multiple of 32.
+MRS_EXPORT int mrs_gemm_act_rows(const void* x_map, const void* w_map, void* out, int T, int N, int K, int act, int ctas, void* stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || N % 32 || act < 0 || act > 2 || ctas < 1 || !x_map || !w_map || !out || ((uintptr_t)out & 15)) return MRS_BAD_ARGUMENT;
+    if (act == 0) return launch<0>(x_map, w_map, out, T, N, K, ctas, stream);
+    if (act == 1) return launch<1>(x_map, w_map, out, T, N, K, ctas, stream);
+    return launch<2>(x_map, w_map, out, T, N, K, ctas, stream);
 }
 
 MRS_EXPORT int mrs_gemm_many_rows_take_error(unsigned int* word) { return mrs_take_error_word(word); }

@@ -895,6 +895,8 @@ def gemm_many_rows_library() -> ctypes.CDLL:
         lib.mrs_gemm_many_rows_map.restype = _c_int
         lib.mrs_gemm_gated_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp]
         lib.mrs_gemm_gated_rows.restype = _c_int
+        lib.mrs_gemm_act_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp]
+        lib.mrs_gemm_act_rows.restype = _c_int
         lib.mrs_gemm_many_rows_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         lib.mrs_gemm_many_rows_take_error.restype = _c_int
         lib.mrs_gemm_many_rows_error_string.argtypes = [_c_int]
@@ -945,6 +947,73 @@ def gemm_gated_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) ->
     del x_keep
     if code != 0:
         raise BackendError(f"gemm_gated_rows: {lib.mrs_gemm_many_rows_error_string(code).decode()} (code {code})")
+
+
+def gemm_act_rows_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """bfloat16, rows of a multiple of 8 elements on 16-byte boundaries, a multiple of 32 weight rows."""
+    return (x.dtype is torch.bfloat16 and weight.dtype is torch.bfloat16 and x.shape[1] % 8 == 0 and weight.shape[0] % 32 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def gemm_act_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out[T, N] = act(x . weight^T) in bfloat16 for any number of rows, the activation (one of ACTIVATIONS, computed in
+    float32 on the float32 sums) in the product's epilogue: the ungated counterpart of `gemm_gated_rows`."""
+    global launch_count
+    t, k = x.shape
+    n = weight.shape[0]
+    _need(x, torch.bfloat16, "activated product input")
+    _need(weight, torch.bfloat16, "activated product weight", (n, k))
+    _need(out, torch.bfloat16, "activated product out", (t, n))
+    if kind not in ACTIVATIONS:
+        raise InvalidRequest(f"activation {kind!r} is not built; known: {sorted(ACTIVATIONS)}")
+    if not gemm_act_rows_supported(x, weight):
+        raise InvalidRequest("the activated product needs K a multiple of 8, N a multiple of 32 and 16-byte alignment")
+    lib = gemm_many_rows_library()
+    x_keep, x_map, w_map = _many_rows_maps_of(lib, x, weight)
+    launch_count += 1
+    code = lib.mrs_gemm_act_rows(x_map, w_map, out.data_ptr(), t, n, k, ACTIVATIONS[kind], sm_count(x.device), _stream())
+    del x_keep
+    if code != 0:
+        raise BackendError(f"gemm_act_rows: {lib.mrs_gemm_many_rows_error_string(code).decode()} (code {code})")
+
+
+_act_rows_choice: dict[tuple, bool] = {}
+
+
+def gemm_act_rows_wins(x: torch.Tensor, weight: torch.Tensor, kind: str) -> bool:
+    """`gemm_gated_rows_wins` for the ungated product: at least GEMM_GATED_ROWS_MIN rows, and ahead of the library's
+    product followed by `activation` when the two were timed for these sizes (once, outside a recording)."""
+    rows = x.shape[0]
+    if rows < GEMM_GATED_ROWS_MIN or not gemm_act_rows_supported(x, weight):
+        return False
+    if not GEMM_GATED_MEASURE:
+        return True
+    n, k = weight.shape
+    key = (x.device, n, k, kind, 1024 * min(-(-rows // 1024), 16))
+    if torch.cuda.is_current_stream_capturing():
+        return _act_rows_choice.get(key, False)
+    if key not in _act_rows_choice:
+        act = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device)
+
+        def own():
+            gemm_act_rows(x, weight, act, kind)
+
+        def library():
+            torch.mm(x, weight.t(), out=act)
+            activation(act, act, kind)
+
+        times = []
+        for run in (own, library):
+            run()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(3):
+                run()
+            end.record()
+            end.synchronize()
+            times.append(start.elapsed_time(end))
+        _act_rows_choice[key] = times[0] <= times[1]
+    return _act_rows_choice[key]
 
 
 def wait_probe(limit_cycles: int = 1 << 16, device=None) -> bool:

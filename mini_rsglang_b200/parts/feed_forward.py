@@ -124,6 +124,11 @@ class DenseMLP(FeedForward):
         self.down = tensors[self.name(self.leaf["down"])].contiguous()
 
     def forward(self, h, ctx):
-        z = linear(plain(h), self.up)
-        kernels.activation(z, z, self.activation)
+        x = plain(h)
+        if kernels.gemm_act_rows_wins(x, self.up, self.activation):      # many rows: the activation in the product's epilogue
+            z = torch.empty((x.shape[0], self.inner), dtype=x.dtype, device=x.device)
+            kernels.gemm_act_rows(x, self.up, z, self.activation)
+        else:
+            z = linear(x, self.up)
+            kernels.activation(z, z, self.activation)
         return linear(z, self.down, out_dtype=torch.float32)

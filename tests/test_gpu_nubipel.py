@@ -244,6 +244,26 @@ def test_activations(kind):
     assert torch.isfinite(out).all() and out[0, 2] == 0 and out[0, 5] == 1e4 and out[0, 6].abs() == 0
 
 
+@pytest.mark.parametrize("kind", ["gelu_erf", "gelu_tanh", "silu"])
+@pytest.mark.parametrize("rows,n,k", [(300, 96, 72), (129, 544, 200), (2048, 512, 256), (1, 32, 64)])
+def test_activation_in_the_epilogue_of_the_product_for_many_rows(kind, rows, n, k):
+    """act(x . w^T) from the tensor-core product whose epilogue applies the activation to the float32 sums, against float64:
+    row and column counts that leave tiles partly empty, a K that is no multiple of the copies' 64 columns."""
+    from mini_rsglang_b200 import kernels
+
+    torch.manual_seed(17)
+    plain = {"gelu_erf": P.gelu_erf, "silu": P.silu,
+             "gelu_tanh": lambda z: 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))}[kind]
+    x = torch.randn(rows, k, device=DEV).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * (2.0 / k ** 0.5)).bfloat16()
+    assert kernels.gemm_act_rows_supported(x, w)
+    out = torch.full((rows, n), 77.0, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_act_rows(x, w, out, kind)
+    kernels.check_device_errors()
+    want = plain(x.double().cpu() @ w.double().cpu().T)
+    assert (out.double().cpu() - want).abs().max() < 8e-3 * max(1.0, want.abs().max().item())
+
+
 def test_scaled_embeddings_and_capped_logits():
     from mini_rsglang_b200 import kernels
 
