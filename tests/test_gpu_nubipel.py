@@ -183,6 +183,27 @@ def test_latent_attention_of_many_heads(folders, tmp_path_factory, mode):
         T.check_rows(got, want, "bfloat16", f"Z bfloat16 {mode} step {step}")
 
 
+def test_a_prompt_of_more_rows_than_a_recorded_step_holds(tmp_path_factory):
+    """2,100 tokens in one step: the step is queued kernel by kernel, the feed-forward's first product takes the kernel for
+    many rows with the activation in its epilogue (the variable makes it the choice whatever the timing says), the
+    chunked attention crosses its chunk's edge twice, the recurrence walks 2,100 tokens from an empty state."""
+    raw = {"architecture": "Nubipel", "vocab": 97, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+           "logit_scale": 0.5, "logit_softcap": 12.0, "layers": [
+               dict(latent(2, 16, 16, 32, 16), mlp=dense(64)),
+               dict(attention(2, 1, 16, 16, 700), mlp=dense(96)),
+               dict(delta(2, 1, 16, 16, 2), mlp=dense(32))]}
+    folder = write_model(str(tmp_path_factory.mktemp("nubipel_long")), raw, 61)
+    config, weights = load_plain(folder)
+    reqs = T.requests_for(raw["vocab"], [2100], seed=12)
+    want = P.forward(config, weights, reqs["r0"])
+    trace = T.trace_whole(reqs)
+    run = T.TraceRun(folder, "bfloat16", str(tmp_path_factory.mktemp("out_long")), T.rounded(2100),
+                     env=dict(os.environ, MRS_GEMM_GATED_ROWS_MIN="2048"), extra=("--page-size", "16"))
+    got = run.step(trace.steps[0], raw["vocab"])
+    assert run.close() == 0
+    T.check_rows(got, torch.stack([want[p] for _, p in trace.rows[0]]), "bfloat16", "a prompt of 2,100 tokens")
+
+
 @pytest.mark.parametrize("name", ["X", "Y"])
 def test_float32_logits_do_not_depend_on_the_cutting(folders, tmp_path_factory, name):
     """The same position whole, decoded, in portions and mixed with other requests on pages and slots used again: within the
