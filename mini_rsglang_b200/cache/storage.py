@@ -46,8 +46,13 @@ def bytes_per_page(needs: list[KVNeed | None], group_of: list[int], group: int, 
 
 class CacheStorage:
     def __init__(self, kv_needs: list[KVNeed | None], state_needs: list[StateNeed | None],
-                 groups: list[CacheGroup], group_of: list[int], max_slots: int, runtime: Runtime):
+                 groups: list[CacheGroup], group_of: list[int], max_slots: int, runtime: Runtime,
+                 embedding_state: StateNeed | None = None):
+        """`embedding_state`: what the embedding keeps of a request between steps, an array [slots, *shape] of its own."""
         self.entries: list[CacheEntry] = []
+        self.embedding_state = None
+        if embedding_state is not None:
+            self.embedding_state = torch.zeros((max_slots, *embedding_state.shape), dtype=embedding_state.dtype, device=runtime.device)
         for need, state, g in zip(kv_needs, state_needs, group_of):
             entry = CacheEntry(group=g)
             if need is not None:
@@ -60,7 +65,7 @@ class CacheStorage:
             self.entries.append(entry)
 
     def bytes(self) -> int:
-        total = 0
+        total = 0 if self.embedding_state is None else self.embedding_state.numel() * self.embedding_state.element_size()
         for e in self.entries:
             for t in (e.k, e.v, e.state):
                 if t is not None:

@@ -100,8 +100,11 @@ def load_engine(args, limits: RuntimeConfig):
 
 
 def shares_prefixes(spec) -> bool:
-    """Whether requests of this model can read one another's pages: every mixer keeps all its keys and no state."""
-    _, blocks, _, _ = spec.build_parts()
+    """Whether requests of this model can read one another's pages: every mixer keeps all its keys and no state, and the
+    embedding keeps nothing of a request either."""
+    embedding, blocks, _, _ = spec.build_parts()
+    if embedding.state_need() is not None:
+        return False
     for block in blocks:
         part = block.cache_part()
         if part is None:

@@ -576,3 +576,173 @@ class NubipelConfig(ModelConfig):
         if self.eos_token_id is not None:
             out["eos_token_id"] = self.eos_token_id
         return out
+
+
+@dataclass
+class MigenexConfig(ModelConfig):
+    """Migenex: a decoder of layers with an RMS norm before and after each branch, whose branches join the stream times a
+    constant.  The mixer is an attention with normed and then rotated heads and capped scores ("attention") or one whose
+    values are its keys as projected, with heads rotated in interleaved pairs and then divided by their root mean square, a
+    sliding window and a gate a value element ("attention_2").  The feed-forward is a gated unit with a relu gate, or routed
+    experts without a gate (the square of relu) whose sigmoid scores multiply what they read, beside a shared expert.  The
+    embedding adds a row of a table of token pairs; a run of layers may be passed several times with the same weights, every
+    pass opened by a product over the stream and the embedding.  config.json gives `vocab`, `width`, `norm.eps`,
+    `residual_mult`, `embedding.{scale, bigram.{buckets, mul_prev, mul_cur}}`, `loop.{start, stop, times}` and, layer by
+    layer, `layers[i].{type, mixer, mlp}`; what may be absent: the table of pairs, the loop, a layer's mask, cap and
+    feed-forward, the shared expert."""
+
+    width: int = 0
+    norm_eps: float = 0.0
+    residual_mult: float = 1.0
+    embedding_scale: float = 1.0
+    bigram: dict | None = None
+    loop: dict | None = None
+    layers: list = None
+
+    MODEL_TYPES: ClassVar[tuple[str, ...]] = ("migenex",)
+    NO_CONTEXT_LIMIT: ClassVar[int] = 1 << 22
+    MIXERS: ClassVar[tuple[str, ...]] = ("attention", "attention_2")
+
+    @classmethod
+    def _mixer(cls, i: int, mixer: dict) -> dict:
+        where = f"layers[{i}].mixer"
+        out = {key: _require(mixer, key, int, where) for key in ("heads", "kv_heads", "dim", "vdim")}
+        out["scale"] = _require(mixer, "scale", float, where)
+        rot = mixer.get("rot")
+        if not isinstance(rot, dict):
+            raise InvalidRequest(f"config.json: {where}.rot must be an object")
+        out["rot"] = {"base": _require(rot, "base", float, "rotary base"), "dims": _require(rot, "dims", int, "rotated elements")}
+        mask = mixer.get("mask")
+        if mask is not None:
+            if not isinstance(mask, dict):
+                raise InvalidRequest(f"config.json: {where}.mask must be an object")
+            out["mask"] = {"size": _require(mask, "size", int, "window")}
+        if mixer.get("softcap") is not None:
+            out["softcap"] = _require(mixer, "softcap", float, "soft cap of the scores")
+        return out
+
+    @classmethod
+    def _mlp(cls, i: int, mlp) -> dict | None:
+        if mlp is None:
+            return None
+        where = f"layers[{i}].mlp"
+        if not isinstance(mlp, dict):
+            raise InvalidRequest(f"config.json: {where} must be null or an object")
+        kind = _require(mlp, "kind", str, "feed-forward kind")
+        if kind == "dense":
+            return {"kind": kind, "ff": _require(mlp, "ff", int, "feed-forward width")}
+        if kind != "moe":
+            raise InvalidRequest(f"config.json: {where}.kind {kind!r}; known: dense, moe")
+        expert, router = mlp.get("expert"), mlp.get("router")
+        if not isinstance(expert, dict) or not isinstance(router, dict):
+            raise InvalidRequest(f"config.json: {where} needs the objects `expert` and `router`")
+        out = {"kind": kind, "expert": {"ff": _require(expert, "ff", int, "expert width")},
+               "router": {"experts": _require(router, "experts", int, "experts"), "top": _require(router, "top", int, "choices")}}
+        shared = mlp.get("shared")
+        if shared is not None:
+            if not isinstance(shared, dict):
+                raise InvalidRequest(f"config.json: {where}.shared must be an object")
+            out["shared"] = {"ff": _require(shared, "ff", int, "shared expert width")}
+        return out
+
+    @classmethod
+    def from_dict(cls, raw: dict) -> "MigenexConfig":
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise InvalidRequest("config.json: missing key `norm` (an object with `eps`)")
+        layers = raw.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise InvalidRequest("config.json: `layers` must be a list of layers")
+        read = []
+        for i, layer in enumerate(layers):
+            if not isinstance(layer, dict):
+                raise InvalidRequest(f"config.json: layers[{i}] must be an object")
+            kind = _require(layer, "type", str, f"mixer of layer {i}")
+            if kind not in cls.MIXERS:
+                raise InvalidRequest(f"config.json: layers[{i}].type {kind!r}; known: {', '.join(cls.MIXERS)}")
+            if not isinstance(layer.get("mixer"), dict):
+                raise InvalidRequest(f"config.json: layers[{i}].mixer must be an object")
+            read.append({"type": kind, "mixer": cls._mixer(i, layer["mixer"]), "mlp": cls._mlp(i, layer.get("mlp"))})
+        embedding = raw.get("embedding") or {}
+        if not isinstance(embedding, dict):
+            raise InvalidRequest("config.json: `embedding` must be an object")
+        bigram = embedding.get("bigram")
+        if bigram is not None:
+            if not isinstance(bigram, dict):
+                raise InvalidRequest("config.json: `embedding.bigram` must be an object")
+            bigram = {key: _require(bigram, key, int, "embedding.bigram") for key in ("buckets", "mul_prev", "mul_cur")}
+        loop = raw.get("loop")
+        if loop is not None:
+            if not isinstance(loop, dict):
+                raise InvalidRequest("config.json: `loop` must be an object")
+            loop = {key: _require(loop, key, int, "loop") for key in ("start", "stop", "times")}
+        cfg = cls(model_type="migenex", architectures=["Migenex"], vocab_size=_require(raw, "vocab", int, "vocabulary"),
+                  max_position_embeddings=int(raw.get("max_position_embeddings") or cls.NO_CONTEXT_LIMIT),
+                  eos_token_id=raw.get("eos_token_id"), width=_require(raw, "width", int, "model width"),
+                  norm_eps=_require(norm, "eps", float, "norm epsilon"),
+                  residual_mult=_require(raw, "residual_mult", float, "branch multiplier") if raw.get("residual_mult") is not None else 1.0,
+                  embedding_scale=_require(embedding, "scale", float, "embedding scale") if embedding.get("scale") is not None else 1.0,
+                  bigram=bigram, loop=loop, layers=read)
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.width <= 0 or self.max_position_embeddings <= 0:
+            raise InvalidRequest("invalid Migenex dimensions: every size must be a positive integer")
+        if not math.isfinite(self.norm_eps) or self.norm_eps <= 0 or not math.isfinite(self.residual_mult) \
+                or not math.isfinite(self.embedding_scale):
+            raise InvalidRequest("invalid normalization parameters, branch multiplier or embedding scale")
+        if self.bigram is not None and (self.bigram["buckets"] <= 0 or self.bigram["mul_prev"] < 0 or self.bigram["mul_cur"] < 0):
+            raise InvalidRequest("embedding.bigram: a positive number of buckets and multipliers that are not negative")
+        if self.loop is not None:
+            lo, hi, times = self.loop["start"], self.loop["stop"], self.loop["times"]
+            if not 0 <= lo < hi <= len(self.layers) or times < 1:
+                raise InvalidRequest("loop: start < stop within the layers, and at least one pass")
+        for i, layer in enumerate(self.layers):
+            m = layer["mixer"]
+            if min(m["heads"], m["kv_heads"], m["dim"], m["vdim"]) <= 0 or m["heads"] % m["kv_heads"] or not m["scale"] > 0:
+                raise InvalidRequest(f"layers[{i}].mixer: sizes and scale must be positive, query heads a multiple of key/value heads")
+            if m["dim"] > 256 or m["vdim"] > 256:
+                raise InvalidRequest(f"layers[{i}].mixer: heads have at most 256 elements")
+            if layer["type"] == "attention_2" and m["vdim"] != m["dim"]:
+                raise InvalidRequest(f"layers[{i}].mixer: values that are the keys have the keys' size (vdim = dim)")
+            if "mask" in m and m["mask"]["size"] <= 0:
+                raise InvalidRequest(f"layers[{i}].mixer.mask.size must be positive")
+            if "softcap" in m and not m["softcap"] > 0:
+                raise InvalidRequest(f"layers[{i}].mixer.softcap must be positive")
+            rot = m["rot"]
+            if rot["dims"] < 0 or rot["dims"] % 2 or rot["dims"] > m["dim"] or not rot["base"] > 0:
+                raise InvalidRequest(f"layers[{i}].mixer.rot: an even number of elements, at most dim, and a positive base")
+            mlp = layer["mlp"]
+            if mlp is None:
+                continue
+            if mlp["kind"] == "dense":
+                if mlp["ff"] <= 0:
+                    raise InvalidRequest(f"layers[{i}].mlp.ff must be positive")
+                continue
+            r = mlp["router"]
+            if not 0 < r["top"] <= r["experts"] or mlp["expert"]["ff"] <= 0:
+                raise InvalidRequest(f"layers[{i}].mlp: experts and choices out of range")
+            if "shared" in mlp and mlp["shared"]["ff"] <= 0:
+                raise InvalidRequest(f"layers[{i}].mlp.shared.ff must be positive")
+        if self.eos_token_id is not None:
+            self.eos_ids()
+
+    def eos_ids(self, folder: str | None = None) -> list[int]:
+        if self.eos_token_id is None and (folder is None or not os.path.exists(os.path.join(folder, "generation_config.json"))):
+            return []                # the design names no end-of-sequence token: generation ends by length
+        return super().eos_ids(folder)
+
+    def to_dict(self) -> dict:
+        embedding = {"scale": self.embedding_scale}
+        if self.bigram is not None:
+            embedding["bigram"] = self.bigram
+        out = {"architecture": "Migenex", "vocab": self.vocab_size, "width": self.width, "norm": {"eps": self.norm_eps},
+               "residual_mult": self.residual_mult, "embedding": embedding, "layers": self.layers}
+        if self.loop is not None:
+            out["loop"] = self.loop
+        if self.max_position_embeddings != self.NO_CONTEXT_LIMIT:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_id is not None:
+            out["eos_token_id"] = self.eos_token_id
+        return out

@@ -188,6 +188,7 @@ LATENT_KERNEL_SOURCES = ("latent_elementwise.cu",)
 EXPERT_KERNEL_SOURCES = ("experts.cu", "experts_mma.cu")
 PARALLEL_KERNEL_SOURCES = ("parallel_elementwise.cu",)
 DELTA_KERNEL_SOURCES = ("delta_rule.cu",)
+ROTARY_KERNEL_SOURCES = ("rotary_store.cu", "stream_entry.cu")
 
 
 def _kernel_group(key: str, name: str, sources: tuple[str, ...]) -> ctypes.CDLL:
@@ -228,6 +229,13 @@ def delta_kernel_library() -> ctypes.CDLL:
     return _kernel_group("delta", "mrs_delta", DELTA_KERNEL_SOURCES)
 
 
+def rotary_kernel_library() -> ctypes.CDLL:
+    """The kernels of rotated and normed heads on their way into the cache, of embeddings with a table of token pairs and
+    of a stream that is joined with another before a product (every size at run time); compiled when a model first needs
+    one of them."""
+    return _kernel_group("rotary", "mrs_rotary", ROTARY_KERNEL_SOURCES)
+
+
 def biased_attention_library() -> ctypes.CDLL:
     """The CUDA-core attention with extras around its scores (every size at run time); compiled at first use."""
     return _kernel_group("attention_biased", "mrs_attention_biased", ("attention_biased.cu",))
@@ -258,6 +266,7 @@ SPECIALISED_BUILDS = tuple((lambda d=d: specialised_kernel_library("attention_mm
     tuple((lambda d=d: specialised_kernel_library("attention_prefill_tc.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128)) + \
     (lambda: specialised_kernel_library("gemm_tc.cu", {}), lambda: specialised_kernel_library("gemm_many_rows.cu", {}),
      hybrid_kernel_library, latent_kernel_library, expert_kernel_library, parallel_kernel_library, delta_kernel_library,
+     rotary_kernel_library,
      biased_attention_library,
      lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 128, "MRS_VALUE_DIM": 128}),
      lambda: specialised_kernel_library("attention_biased_mma.cu", {"MRS_HEAD_DIM": 64, "MRS_VALUE_DIM": 32}),

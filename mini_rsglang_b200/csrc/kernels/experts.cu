@@ -2,15 +2,19 @@
 //
 //   moe_route      float32 router logits [tokens, all experts (+ 1 gate of the shared expert)] -> scores by softmax
 //                  (or sigmoid) over all experts, the `top` largest of score + correction (ties: the lower number),
-//                  their weights score / (sum of the chosen scores + 1e-20) * scale, sigmoid of the shared gate
+//                  their weights score / (sum of the chosen scores + 1e-20) * scale (or, not normalised, score * scale),
+//                  sigmoid of the shared gate
 //   moe_align      the (token, choice) pairs that go to a routed expert, listed expert by expert, every expert's run
 //                  filled up to whole tiles of `tile` rows (-1), the expert of every tile (-1: unused) and, behind
 //                  them, the number of tiles in use (the runs are packed from the front);
 //                  experts numbered from `routed` on have no weights (they hand their input on) and get no rows
-//   moe_gather_rows  the listed pairs' input rows, in the order of the lists (zeros where a run is filled up): the
-//                  matrix that the product for many rows reads with bulk tensor copies
+//   moe_gather_rows  the listed pairs' input rows, in the order of the lists (zeros where a run is filled up), each times
+//                  its pair's weight if weights are given: the matrix that the product for many rows reads with bulk
+//                  tensor copies, and the input of experts whose weight multiplies what they read
 //   moe_up / moe_down   the two products of the gated unit over those tiles, on the CUDA cores in float32 sums:
-//                  act[row] = silu(W_gate[e] x) * (W_up[e] x),  y[pair] = W_down[e] act[row];
+//                  act[row] = silu(W_gate[e] x) * (W_up[e] x),  y[pair] = W_down[e] act[row]; for experts without a gate
+//                  the first product is the ungated one over gathered rows with an activation on its sums, written at the
+//                  rows' places in the lists (`act` >= 0): act[row] = activation(W_up[e] x_rows[row]);
 //                  one kernel for every size (the 32-bit path), one for few rows an expert (decode steps: the
 //                  weights streamed once); the tensor-core versions are experts_mma.cu and experts_tc.cu
 //   moe_combine    out[token] = sum over its choices of weight * (y[pair] or, for an expert without weights, the
@@ -18,13 +22,14 @@
 //
 // A row's result depends on its own pair alone: which other rows share its tile, and the order of a run, do not enter.
 #include "common.cuh"
+#include "activations.cuh"
 
 namespace {
 
 // One warp a token.  Dynamic shared memory: warps * 2 * all floats (scores, choice scores).
 __global__ void moe_route_kernel(const float* __restrict__ logits, int stride, const float* __restrict__ correction,
                                  int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ shared_gate, int tokens,
-                                 int all, int top, float scale, int sigmoid_scores, int has_shared) {
+                                 int all, int top, float scale, int sigmoid_scores, int has_shared, int normalize) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float route_smem[];
@@ -71,8 +76,13 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int stride, c
         }
         __syncwarp();
     }
-    if (lane < top) weights[(size_t)t * top + lane] = weights[(size_t)t * top + lane] / (picked_sum + 1e-20f) * scale;
-    for (int k = 32 + lane; k < top; k += 32) weights[(size_t)t * top + k] = weights[(size_t)t * top + k] / (picked_sum + 1e-20f) * scale;
+    const float factor = normalize ? scale / (picked_sum + 1e-20f) : scale;          // not normalised: the scores themselves
+    if (normalize) {
+        if (lane < top) weights[(size_t)t * top + lane] = weights[(size_t)t * top + lane] / (picked_sum + 1e-20f) * scale;
+        for (int k = 32 + lane; k < top; k += 32) weights[(size_t)t * top + k] = weights[(size_t)t * top + k] / (picked_sum + 1e-20f) * scale;
+    } else if (scale != 1.0f) {
+        for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= factor;
+    }
     if (has_shared && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-z[all]));
 }
 
@@ -120,7 +130,7 @@ constexpr int SIMT_TM = 32, SIMT_TN = 64, SIMT_TK = 32;
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_product_simt_kernel(const T* __restrict__ x, const int* __restrict__ sorted_rows,
                                                                const int* __restrict__ tile_expert, const T* __restrict__ weight,
-                                                               T* __restrict__ out, int n, int k, int top, int block) {
+                                                               T* __restrict__ out, int n, int k, int top, int block, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int expert = tile_expert[blockIdx.x];
@@ -173,7 +183,7 @@ __global__ void __launch_bounds__(256) moe_product_simt_kernel(const T* __restri
         const int r = ty + 16 * i;
         const int pair = row_of[r];
         if (pair < 0) continue;
-        T* dst = out + (size_t)(GATED ? row0 + r : pair) * n;
+        T* dst = out + (size_t)(GATED || act >= 0 ? row0 + r : pair) * n;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int col = col0 + tx + 16 * j;
@@ -182,6 +192,8 @@ __global__ void __launch_bounds__(256) moe_product_simt_kernel(const T* __restri
             if (GATED) {
                 const float g = to_float(from_float<T>(v)), u = to_float(from_float<T>(acc[1][i][j]));   // the projections' own rounding
                 v = g / (1.0f + expf(-g)) * u;
+            } else if (act >= 0) {
+                v = mrs_activate(v, act);
             }
             dst[col] = from_float<T>(v);
         }
@@ -217,7 +229,7 @@ template <> struct Piece<bf16> {
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(32 * ROWS_WARPS) moe_product_rows_kernel(const T* __restrict__ x, const int* __restrict__ sorted_rows,
                                                                             const int* __restrict__ tile_expert, const T* __restrict__ weight,
-                                                                            T* __restrict__ out, int n, int k, int top, int block) {
+                                                                            T* __restrict__ out, int n, int k, int top, int block, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int expert = tile_expert[blockIdx.x];
@@ -279,9 +291,11 @@ __global__ void __launch_bounds__(32 * ROWS_WARPS) moe_product_rows_kernel(const
             if (GATED) {
                 const float g = to_float(from_float<T>(v)), u = to_float(from_float<T>(warp_sum(acc[j][NB - 1][r])));   // the projections' own rounding
                 v = g / (1.0f + expf(-g)) * u;
+            } else if (act >= 0) {
+                v = mrs_activate(v, act);
             }
             const int pair = row_of[r];
-            if (lane == 0 && col < n && pair >= 0) out[(size_t)(GATED ? row0 + r : pair) * n + col] = from_float<T>(v);
+            if (lane == 0 && col < n && pair >= 0) out[(size_t)(GATED || act >= 0 ? row0 + r : pair) * n + col] = from_float<T>(v);
         }
     }
 }
@@ -296,6 +310,19 @@ __global__ void moe_gather_rows_kernel(const bf16* __restrict__ x, const int* __
     for (int i = threadIdx.x; i < k / 8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0u, 0u, 0u, 0u);
 }
 
+// The same with every row multiplied by its pair's weight (float32 product, rounded once), any size and both dtypes.
+template <typename T>
+__global__ void moe_gather_scaled_rows_kernel(const T* __restrict__ x, const int* __restrict__ sorted_rows, const float* __restrict__ weights,
+                                              T* __restrict__ out, int k, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pair = sorted_rows[blockIdx.x];
+    const T* src = x + (size_t)(pair < 0 ? 0 : pair / top) * k;
+    const float w = pair >= 0 ? weights[pair] : 0.0f;
+    T* dst = out + (size_t)blockIdx.x * k;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) dst[i] = from_float<T>(pair >= 0 ? to_float(src[i]) * w : 0.0f);
+}
+
 // One block a token.
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict__ h, const T* __restrict__ shared_out,
@@ -304,13 +331,13 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict_
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const float gate = shared_out ? shared_gate[t] : 0.0f;
+    const float gate = shared_out ? (shared_gate ? shared_gate[t] : 1.0f) : 0.0f;        // no gates: the shared expert counts fully
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = 0.0f;
         for (int c = 0; c < top; ++c) {
             const int pair = t * top + c;
             const float part = chosen[pair] < routed ? to_float(y[(size_t)pair * width + i]) : to_float(h[(size_t)t * width + i]);
-            v += weights[pair] * part;
+            v += (weights ? weights[pair] : 1.0f) * part;                                  // no weights: they were applied before
         }
         if (shared_out) v += gate * to_float(shared_out[(size_t)t * width + i]);
         out[(size_t)t * width + i] = from_float<T>(v);
@@ -342,14 +369,14 @@ __global__ void moe_combine_vec_kernel(const T* __restrict__ y, const T* __restr
     pdl_wait();
     constexpr int V = Piece<T>::N;
     const int t = blockIdx.x;
-    const float gate = shared_out ? shared_gate[t] : 0.0f;
+    const float gate = shared_out ? (shared_gate ? shared_gate[t] : 1.0f) : 0.0f;        // no gates: the shared expert counts fully
     for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
         float v[V] = {};
         float own[V];
         bool have_own = false;
         for (int c = 0; c < top; ++c) {
             const int pair = t * top + c;
-            const float weight = weights[pair];
+            const float weight = weights ? weights[pair] : 1.0f;
             float part[V];
             if (chosen[pair] < routed) {
                 Piece<T>::load(y + (size_t)pair * width + i, part);
@@ -376,7 +403,7 @@ __global__ void moe_combine_vec_kernel(const T* __restrict__ y, const T* __restr
 MRS_EXPORT int mrs_moe_simt_tile() { return SIMT_TM; }
 
 MRS_EXPORT int mrs_moe_route(const float* logits, int stride, const float* correction, int* chosen, float* weights, float* shared_gate,
-                             int tokens, int all, int top, float scale, int sigmoid_scores, int has_shared, void* stream) {
+                             int tokens, int all, int top, float scale, int sigmoid_scores, int has_shared, int normalize, void* stream) {
     if (tokens <= 0) return 0;
     if (all <= 0 || top <= 0 || top > all || stride < all + (has_shared ? 1 : 0) || (has_shared && !shared_gate)) return MRS_BAD_ARGUMENT;
     int warps = 4;
@@ -384,7 +411,7 @@ MRS_EXPORT int mrs_moe_route(const float* logits, int stride, const float* corre
     const size_t smem = (size_t)warps * 2 * all * sizeof(float);
     if (smem > 48 * 1024) return MRS_BAD_ARGUMENT;
     MRS_LAUNCH(moe_route_kernel, (tokens + warps - 1) / warps, 32 * warps, smem, stream, logits, stride, correction, chosen, weights,
-               shared_gate, tokens, all, top, scale, sigmoid_scores, has_shared);
+               shared_gate, tokens, all, top, scale, sigmoid_scores, has_shared, normalize);
     MRS_RETURN_LAUNCH_STATUS();
 }
 
@@ -404,15 +431,17 @@ MRS_EXPORT int mrs_moe_align(const int* chosen, int pairs, int routed, int tile,
 }
 
 // gated != 0: x [tokens, k], weight [experts, 2 n, k], out [capacity, n]; else x [capacity, k], weight [experts, n, k],
-// out [pairs, n].  Lists in tiles of mrs_moe_simt_tile() rows.  `block` > 0 (gated): gate and up rows alternate in blocks.
+// out [pairs, n], or with act >= 0 (an activation's number) out [capacity, n] = activation of the sums, at the rows' places.
+// Lists in tiles of mrs_moe_simt_tile() rows.  `block` > 0 (gated): gate and up rows alternate in blocks.
 MRS_EXPORT int mrs_moe_product_simt(int is_bf16, int gated, const void* x, const int* sorted_rows, const int* tile_expert,
-                                    const void* weight, void* out, int capacity, int n, int k, int top, int block, void* stream) {
+                                    const void* weight, void* out, int capacity, int n, int k, int top, int block, int act, void* stream) {
     if (capacity <= 0) return 0;
-    if (capacity % SIMT_TM || n <= 0 || k <= 0 || top <= 0 || block < 0 || (block && n % block)) return MRS_BAD_ARGUMENT;
+    if (capacity % SIMT_TM || n <= 0 || k <= 0 || top <= 0 || block < 0 || (block && n % block) || act > 4 || (gated && act >= 0))
+        return MRS_BAD_ARGUMENT;
     const dim3 grid(capacity / SIMT_TM, (n + SIMT_TN - 1) / SIMT_TN);
 #define MRS_MOE_SIMT(T, GATED)                                                                                                   \
     MRS_LAUNCH((moe_product_simt_kernel<T, GATED>), grid, 256, 0, stream, (const T*)x, sorted_rows, tile_expert, (const T*)weight, \
-               (T*)out, n, k, top, block)
+               (T*)out, n, k, top, block, act)
     if (is_bf16) {
         if (gated) MRS_MOE_SIMT(bf16, true); else MRS_MOE_SIMT(bf16, false);
     } else {
@@ -427,15 +456,16 @@ MRS_EXPORT int mrs_moe_rows_tile() { return ROWS_TM; }
 // As mrs_moe_product_simt for lists in tiles of mrs_moe_rows_tile() rows: few rows an expert.  k * sizeof(T) a multiple of 16,
 // x, weight on 16-byte boundaries.
 MRS_EXPORT int mrs_moe_product_rows(int is_bf16, int gated, const void* x, const int* sorted_rows, const int* tile_expert,
-                                    const void* weight, void* out, int capacity, int n, int k, int top, int block, void* stream) {
+                                    const void* weight, void* out, int capacity, int n, int k, int top, int block, int act, void* stream) {
     if (capacity <= 0) return 0;
     if (capacity % ROWS_TM || n <= 0 || k <= 0 || k % (is_bf16 ? 8 : 4) || top <= 0 || block < 0 || (block && (!gated || n % block)) ||
+        act > 4 || (gated && act >= 0) ||
         (((uintptr_t)x | (uintptr_t)weight) & 15))
         return MRS_BAD_ARGUMENT;
     const dim3 grid(capacity / ROWS_TM, (n + ROWS_WARPS * ROWS_J - 1) / (ROWS_WARPS * ROWS_J));
 #define MRS_MOE_ROWS(T, GATED)                                                                                                             \
     MRS_LAUNCH((moe_product_rows_kernel<T, GATED>), grid, 32 * ROWS_WARPS, 0, stream, (const T*)x, sorted_rows, tile_expert, (const T*)weight, \
-               (T*)out, n, k, top, block)
+               (T*)out, n, k, top, block, act)
     if (is_bf16) {
         if (gated) MRS_MOE_ROWS(bf16, true); else MRS_MOE_ROWS(bf16, false);
     } else {
@@ -453,10 +483,22 @@ MRS_EXPORT int mrs_moe_gather_rows(const void* x, const int* sorted_rows, void* 
     MRS_RETURN_LAUNCH_STATUS();
 }
 
+// out [capacity, k] = x[pair / top] * weights[pair] for the listed pairs, zeros for -1; any k, both dtypes.
+MRS_EXPORT int mrs_moe_gather_scaled_rows(int is_bf16, const void* x, const int* sorted_rows, const float* weights, void* out, int capacity,
+                                          int k, int top, void* stream) {
+    if (capacity <= 0) return 0;
+    if (k <= 0 || top <= 0 || !weights) return MRS_BAD_ARGUMENT;
+    if (is_bf16)
+        MRS_LAUNCH(moe_gather_scaled_rows_kernel<bf16>, capacity, 128, 0, stream, (const bf16*)x, sorted_rows, weights, (bf16*)out, k, top);
+    else
+        MRS_LAUNCH(moe_gather_scaled_rows_kernel<float>, capacity, 128, 0, stream, (const float*)x, sorted_rows, weights, (float*)out, k, top);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
 MRS_EXPORT int mrs_moe_combine(int is_bf16, const void* y, const void* h, const void* shared_out, const int* chosen, const float* weights,
                                const float* shared_gate, void* out, int tokens, int width, int top, int routed, void* stream) {
     if (tokens <= 0) return 0;
-    if (width <= 0 || top <= 0 || (shared_out && !shared_gate)) return MRS_BAD_ARGUMENT;
+    if (width <= 0 || top <= 0) return MRS_BAD_ARGUMENT;
     const int threads = width >= 1024 ? 256 : 128;
     const bool aligned = (((uintptr_t)y | (uintptr_t)h | (uintptr_t)shared_out | (uintptr_t)out) & 15) == 0;
     if (aligned && width % (is_bf16 ? 8 : 4) == 0) {

@@ -4,6 +4,7 @@
 // columns side by side and stores silu(gate) * up; the rows of the first product are gathered by token, the rows of
 // the second are scattered to their (token, choice) pair.  K must be a multiple of 8 (rows on 16-byte boundaries).
 #include "common.cuh"
+#include "activations.cuh"
 
 namespace {
 
@@ -33,7 +34,7 @@ __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(_
 template <bool GATED>
 __global__ void __launch_bounds__(THREADS) moe_product_mma_kernel(const bf16* __restrict__ x, const int* __restrict__ sorted_rows,
                                                                   const int* __restrict__ tile_expert, const bf16* __restrict__ weight,
-                                                                  bf16* __restrict__ out, int n, int k, int top, int block) {
+                                                                  bf16* __restrict__ out, int n, int k, int top, int block, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int expert = tile_expert[blockIdx.x];
@@ -114,7 +115,7 @@ __global__ void __launch_bounds__(THREADS) moe_product_mma_kernel(const bf16* __
         const int r = warp * 16 + (lane >> 2) + 8 * rr;
         const int pair = row_of[r];
         if (pair < 0) continue;
-        bf16* dst = out + (size_t)(GATED ? row0 + r : pair) * n;
+        bf16* dst = out + (size_t)(GATED || act >= 0 ? row0 + r : pair) * n;
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt)
 #pragma unroll
@@ -125,6 +126,8 @@ __global__ void __launch_bounds__(THREADS) moe_product_mma_kernel(const bf16* __
                 if (GATED) {
                     const float g = round_bf16(v), u = round_bf16(acc[NB - 1][nt][2 * rr + e]);     // the projections' own rounding
                     v = g / (1.0f + expf(-g)) * u;
+                } else if (act >= 0) {
+                    v = mrs_activate(v, act);
                 }
                 dst[col] = __float2bfloat16_rn(v);
             }
@@ -137,12 +140,12 @@ template <bool GATED> constexpr size_t smem_bytes() { return (size_t)(2 * BM * B
 
 MRS_EXPORT int mrs_moe_mma_tile() { return BM; }
 
-// As mrs_moe_product_simt (`block` too), bfloat16 only, lists in tiles of mrs_moe_mma_tile() rows, k a multiple of 8.
+// As mrs_moe_product_simt (`block` and `act` too), bfloat16 only, lists in tiles of mrs_moe_mma_tile() rows, k a multiple of 8.
 MRS_EXPORT int mrs_moe_product_mma(int gated, const void* x, const int* sorted_rows, const int* tile_expert, const void* weight, void* out,
-                                   int capacity, int n, int k, int top, int block, void* stream) {
+                                   int capacity, int n, int k, int top, int block, int act, void* stream) {
     if (capacity <= 0) return 0;
     if (capacity % BM || n <= 0 || k <= 0 || k % 8 || top <= 0 || (((uintptr_t)x | (uintptr_t)weight) & 15) || block < 0 ||
-        (block && (!gated || n % block)))
+        (block && (!gated || n % block)) || act > 4 || (gated && act >= 0))
         return MRS_BAD_ARGUMENT;
     static bool configured = false;
     if (!configured) {
@@ -155,9 +158,9 @@ MRS_EXPORT int mrs_moe_product_mma(int gated, const void* x, const int* sorted_r
     const dim3 grid(capacity / BM, (n + BN - 1) / BN);
     if (gated)
         MRS_LAUNCH(moe_product_mma_kernel<true>, grid, THREADS, smem_bytes<true>(), stream, (const bf16*)x, sorted_rows, tile_expert,
-                   (const bf16*)weight, (bf16*)out, n, k, top, block);
+                   (const bf16*)weight, (bf16*)out, n, k, top, block, act);
     else
         MRS_LAUNCH(moe_product_mma_kernel<false>, grid, THREADS, smem_bytes<false>(), stream, (const bf16*)x, sorted_rows, tile_expert,
-                   (const bf16*)weight, (bf16*)out, n, k, top, block);
+                   (const bf16*)weight, (bf16*)out, n, k, top, block, act);
     MRS_RETURN_LAUNCH_STATUS();
 }

@@ -13,6 +13,7 @@
 // persistent; tiles that share a weight tile are taken by neighbouring CTAs at the same time.  Every wait is bounded
 // (tma.cuh).
 #include "tcgen05.cuh"
+#include "activations.cuh"
 
 namespace {
 
@@ -26,7 +27,7 @@ constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES 
 template <bool GATED>
 __global__ void __launch_bounds__(THREADS, 1) moe_product_tc_kernel(
     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, const int* __restrict__ tile_expert,
-    const int* __restrict__ sorted_rows, bf16* __restrict__ out, int m_tiles_all, int N, int K) {
+    const int* __restrict__ sorted_rows, bf16* __restrict__ out, int m_tiles_all, int N, int K, int act) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -160,7 +161,7 @@ __global__ void __launch_bounds__(THREADS, 1) moe_product_tc_kernel(
                     }
                 }
             } else {
-                bf16* dst = out + (size_t)(pair < 0 ? 0 : pair) * N + n0;
+                bf16* dst = out + (size_t)(pair < 0 ? 0 : (act >= 0 ? m0 + row : pair)) * N + n0;
 #pragma unroll
                 for (int c = 0; c < BN; c += 32) {
                     float v[32];
@@ -173,7 +174,8 @@ __global__ void __launch_bounds__(THREADS, 1) moe_product_tc_kernel(
                             uint32_t w[4];
 #pragma unroll
                             for (int p = 0; p < 4; ++p) {
-                                __nv_bfloat162 two = __floats2bfloat162_rn(v[e + 2 * p], v[e + 2 * p + 1]);
+                                __nv_bfloat162 two = act >= 0 ? __floats2bfloat162_rn(mrs_activate(v[e + 2 * p], act), mrs_activate(v[e + 2 * p + 1], act))
+                                                              : __floats2bfloat162_rn(v[e + 2 * p], v[e + 2 * p + 1]);
                                 w[p] = *reinterpret_cast<uint32_t*>(&two);
                             }
                             *reinterpret_cast<uint4*>(dst + c + e) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -211,12 +213,13 @@ MRS_EXPORT int mrs_moe_tc_map(const void* base, long long rows, long long cols, 
 // gated != 0: x_map over the gathered rows [capacity, K], w_map over [experts * N, K] with, in every block of 128 rows,
 // 64 gate rows and then the 64 matching up rows (N a multiple of 128), out [capacity, N / 2] = silu(gate) * up.
 // Else: x_map over [capacity, K], w_map over [experts * N, K] (N a multiple of 8), out [pairs, N] written at the rows'
-// pairs.  tile_expert [capacity / 128 + 1] as mrs_moe_align leaves it for tiles of 128 rows; `ctas`: the GPU's SMs.
+// pairs; or, with act >= 0 (an activation's number), out [capacity, N] = activation of the sums, at the rows' places.
+// tile_expert [capacity / 128 + 1] as mrs_moe_align leaves it for tiles of 128 rows; `ctas`: the GPU's SMs.
 MRS_EXPORT int mrs_moe_product_tc(int gated, const void* x_map, const void* w_map, const int* tile_expert, const int* sorted_rows,
-                                  void* out, int capacity, int N, int K, int ctas, void* stream) {
+                                  void* out, int capacity, int N, int K, int act, int ctas, void* stream) {
     if (capacity <= 0) return 0;
     if (capacity % BM || K <= 0 || K % 8 || N <= 0 || (gated ? N % 128 : N % 8) || ctas < 1 || !x_map || !w_map || !out ||
-        ((uintptr_t)out & 15))
+        ((uintptr_t)out & 15) || act > 4 || (gated && act >= 0))
         return MRS_BAD_ARGUMENT;
     static bool configured = false;
     if (!configured) {
@@ -230,10 +233,10 @@ MRS_EXPORT int mrs_moe_product_tc(int gated, const void* x_map, const void* w_ma
     const int grid = (int)(ctas < tiles ? ctas : tiles);
     if (gated)
         MRS_LAUNCH(moe_product_tc_kernel<true>, grid, THREADS, SMEM_BYTES, stream, *reinterpret_cast<const CUtensorMap*>(x_map),
-                   *reinterpret_cast<const CUtensorMap*>(w_map), tile_expert, sorted_rows, (bf16*)out, m_tiles, N, K);
+                   *reinterpret_cast<const CUtensorMap*>(w_map), tile_expert, sorted_rows, (bf16*)out, m_tiles, N, K, act);
     else
         MRS_LAUNCH(moe_product_tc_kernel<false>, grid, THREADS, SMEM_BYTES, stream, *reinterpret_cast<const CUtensorMap*>(x_map),
-                   *reinterpret_cast<const CUtensorMap*>(w_map), tile_expert, sorted_rows, (bf16*)out, m_tiles, N, K);
+                   *reinterpret_cast<const CUtensorMap*>(w_map), tile_expert, sorted_rows, (bf16*)out, m_tiles, N, K, act);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

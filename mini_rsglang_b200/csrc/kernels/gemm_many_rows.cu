@@ -34,10 +34,13 @@ constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES 
 __device__ __forceinline__ float activate(float z, int kind) {
     if (kind == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
     if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    if (kind == 3) return fmaxf(z, 0.0f);
+    if (kind == 4) return fmaxf(z, 0.0f) * fmaxf(z, 0.0f);
     return z / (1.0f + expf(-z));
 }
 
-// ACT < 0: the gated product; 0, 1, 2: the plain product with gelu (error function), gelu (tanh) or silu on every sum.
+// ACT < 0: the gated product (-1: silu(gate) * up, -2: relu(gate) * up); 0 to 4: the plain product with gelu (error
+// function), gelu (tanh), silu, relu or the square of relu on every sum.
 template <int ACT>
 __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
     const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, bf16* __restrict__ out, int T, int N, int K) {
@@ -182,8 +185,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
 #pragma unroll
                             for (int p = 0; p < 4; ++p) {
                                 const float g0 = g[e + 2 * p], g1 = g[e + 2 * p + 1];
-                                __nv_bfloat162 pair = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u[e + 2 * p],
-                                                                            g1 / (1.0f + __expf(-g1)) * u[e + 2 * p + 1]);
+                                __nv_bfloat162 pair = ACT == -2
+                                    ? __floats2bfloat162_rn(fmaxf(g0, 0.0f) * u[e + 2 * p], fmaxf(g1, 0.0f) * u[e + 2 * p + 1])
+                                    : __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u[e + 2 * p],
+                                                            g1 / (1.0f + __expf(-g1)) * u[e + 2 * p + 1]);
                                 w[p] = *reinterpret_cast<uint32_t*>(&pair);
                             }
                             *reinterpret_cast<uint4*>(dst + block * 64 + c + e) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -231,21 +236,27 @@ MRS_EXPORT int mrs_gemm_many_rows_map(const void* base, long long rows, long lon
     return mrs_make_tensor_map_bf16(reinterpret_cast<CUtensorMap*>(map_out), base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-// out[T, N / 2] = silu(x . gate^T) * (x . up^T), bfloat16; w [N, K] holds in every block of 128 rows 64 gate rows and
+// out[T, N / 2] = act(x . gate^T) * (x . up^T), bfloat16, act silu (gate_act 2) or relu (3); w [N, K] holds in every block of 128 rows 64 gate rows and
 // then the 64 matching up rows (N a multiple of 128).  `x_map`: map of x [T, K] with boxes of 128 rows; `w_map`: map
 // of w with boxes of 256 rows.  `ctas`: the GPU's SMs.
-MRS_EXPORT int mrs_gemm_gated_rows(const void* x_map, const void* w_map, void* out, int T, int N, int K, int ctas, void* stream) {
+MRS_EXPORT int mrs_gemm_gated_rows(const void* x_map, const void* w_map, void* out, int T, int N, int K, int gate_act, int ctas,
+                                   void* stream) {
     if (T <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 || N % 128 || ctas < 1 || !x_map || !w_map || !out || ((uintptr_t)out & 15)) return MRS_BAD_ARGUMENT;
+    if (K <= 0 || K % 8 || N % 128 || ctas < 1 || !x_map || !w_map || !out || ((uintptr_t)out & 15) || (gate_act != 2 && gate_act != 3))
+        return MRS_BAD_ARGUMENT;
+    if (gate_act == 3) return launch<-2>(x_map, w_map, out, T, N, K, ctas, stream);
     return launch<-1>(x_map, w_map, out, T, N, K, ctas, stream);
 }
 
-// out[T, N] = act(x . w^T) in bfloat16; act 0: gelu with the error function, 1: gelu with tanh, 2: silu.  N a multiple of 32.
+// out[T, N] = act(x . w^T) in bfloat16; act 0: gelu with the error function, 1: gelu with tanh, 2: silu, 3: relu, 4: the
+// square of relu.  N a multiple of 32.
 MRS_EXPORT int mrs_gemm_act_rows(const void* x_map, const void* w_map, void* out, int T, int N, int K, int act, int ctas, void* stream) {
     if (T <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 || N % 32 || act < 0 || act > 2 || ctas < 1 || !x_map || !w_map || !out || ((uintptr_t)out & 15)) return MRS_BAD_ARGUMENT;
+    if (K <= 0 || K % 8 || N % 32 || act < 0 || act > 4 || ctas < 1 || !x_map || !w_map || !out || ((uintptr_t)out & 15)) return MRS_BAD_ARGUMENT;
     if (act == 0) return launch<0>(x_map, w_map, out, T, N, K, ctas, stream);
     if (act == 1) return launch<1>(x_map, w_map, out, T, N, K, ctas, stream);
+    if (act == 3) return launch<3>(x_map, w_map, out, T, N, K, ctas, stream);
+    if (act == 4) return launch<4>(x_map, w_map, out, T, N, K, ctas, stream);
     return launch<2>(x_map, w_map, out, T, N, K, ctas, stream);
 }
 

@@ -5,14 +5,14 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------
-// stream += rmsnorm(branch) * w_post;  out = rmsnorm(stream) * w_next   (w_next may be null: sum only)
+// stream += mult * rmsnorm(branch) * w_post;  out = rmsnorm(stream) * w_next   (w_next may be null: sum only)
 // branch float32 [rows, width] (a product's float32 sums), stream float32, out T.
 // One block a row; the row is read three times from L1/L2.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void postnorm_add_norm_kernel(float* __restrict__ stream, const float* __restrict__ branch,
                                          const float* __restrict__ w_post, const float* __restrict__ w_next, float eps_post,
-                                         float eps_next, T* __restrict__ out, int width) {
+                                         float eps_next, T* __restrict__ out, int width, float mult) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[33];
@@ -21,7 +21,7 @@ __global__ void postnorm_add_norm_kernel(float* __restrict__ stream, const float
     const float* a = branch + r * width;
     float sum = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) sum += a[i] * a[i];
-    const float scale_a = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps_post);
+    const float scale_a = mult / sqrtf(block_sum(sum, scratch) / (float)width + eps_post);
     sum = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float v = res[i] + a[i] * scale_a * w_post[i];
@@ -51,7 +51,7 @@ template <> __device__ __forceinline__ void st4<bf16>(bf16* p, float4 v) {
 template <typename T>
 __global__ void postnorm_add_norm_kept_kernel(float* __restrict__ stream, const float* __restrict__ branch,
                                               const float* __restrict__ w_post, const float* __restrict__ w_next, float eps_post,
-                                              float eps_next, T* __restrict__ out, int width) {
+                                              float eps_next, T* __restrict__ out, int width, float mult) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[33];
@@ -73,7 +73,7 @@ __global__ void postnorm_add_norm_kept_kernel(float* __restrict__ stream, const 
         rv[j] = i < width ? ld4(res + i) : zero;
         wv[j] = i < width ? ld4(w_post + i) : zero;
     }
-    const float scale_a = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps_post);
+    const float scale_a = mult / sqrtf(block_sum(sum, scratch) / (float)width + eps_post);
     sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < NORM_KEEP; ++j) {
@@ -103,7 +103,7 @@ __global__ void postnorm_add_norm_kept_kernel(float* __restrict__ stream, const 
 }
 
 MRS_EXPORT int mrs_postnorm_add_norm(int is_bf16, float* stream, const float* branch, const float* w_post, const float* w_next,
-                                     float eps_post, float eps_next, void* out, int rows, int width, void* s) {
+                                     float eps_post, float eps_next, void* out, int rows, int width, float mult, void* s) {
     if (rows <= 0) return 0;
     if (width <= 0) return MRS_BAD_ARGUMENT;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
@@ -112,15 +112,15 @@ MRS_EXPORT int mrs_postnorm_add_norm(int is_bf16, float* stream, const float* br
         int kept_threads = ((width / 4 + NORM_KEEP - 1) / NORM_KEEP + 31) / 32 * 32;      // the row fits the block's registers
         if (kept_threads < 64) kept_threads = 64;
         if (is_bf16)
-            MRS_LAUNCH(postnorm_add_norm_kept_kernel<bf16>, rows, kept_threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (bf16*)out, width);
+            MRS_LAUNCH(postnorm_add_norm_kept_kernel<bf16>, rows, kept_threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (bf16*)out, width, mult);
         else
-            MRS_LAUNCH(postnorm_add_norm_kept_kernel<float>, rows, kept_threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (float*)out, width);
+            MRS_LAUNCH(postnorm_add_norm_kept_kernel<float>, rows, kept_threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (float*)out, width, mult);
         MRS_RETURN_LAUNCH_STATUS();
     }
     if (is_bf16)
-        MRS_LAUNCH(postnorm_add_norm_kernel<bf16>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (bf16*)out, width);
+        MRS_LAUNCH(postnorm_add_norm_kernel<bf16>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (bf16*)out, width, mult);
     else
-        MRS_LAUNCH(postnorm_add_norm_kernel<float>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (float*)out, width);
+        MRS_LAUNCH(postnorm_add_norm_kernel<float>, rows, threads, 0, s, stream, branch, w_post, w_next, eps_post, eps_next, (float*)out, width, mult);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

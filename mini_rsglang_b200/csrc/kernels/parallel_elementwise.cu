@@ -93,7 +93,29 @@ __global__ void add_branches_norm_kept_kernel(float* __restrict__ stream, const 
 __device__ __forceinline__ float activate(float z, int kind) {
     if (kind == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
     if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    if (kind == 3) return fmaxf(z, 0.0f);
+    if (kind == 4) return fmaxf(z, 0.0f) * fmaxf(z, 0.0f);
     return z / (1.0f + expf(-z));
+}
+
+// A gated unit's inner rows: out = act(gate) * up over `gate_up` [tokens, 2 * inter]: all gate columns and then all up
+// columns (block 0), or blocks of `block` gate columns each followed by the matching up columns (inter a multiple of
+// block).  A thread keeps its two columns and walks down the tokens.
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens, int inter, int kind, int block) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
+    if (c >= inter) return;
+    const bool pair = c + 1 < inter;
+    const int g0 = block ? c / block * 2 * block + c % block : c, u0 = g0 + (block ? block : inter);
+    const int g1 = block ? (c + 1) / block * 2 * block + (c + 1) % block : c + 1, u1 = g1 + (block ? block : inter);
+    for (int t = blockIdx.y; t < tokens; t += gridDim.y) {
+        const T* row = gate_up + (size_t)t * 2 * inter;
+        T* o = out + (size_t)t * inter;
+        o[c] = from_float<T>(activate(to_float(row[g0]), kind) * to_float(row[u0]));
+        if (pair) o[c + 1] = from_float<T>(activate(to_float(row[g1]), kind) * to_float(row[u1]));
+    }
 }
 
 template <typename T>
@@ -156,7 +178,7 @@ MRS_EXPORT int mrs_add_branches_norm(int is_bf16, float* stream, const float* a,
 
 MRS_EXPORT int mrs_activation(int is_bf16, const void* in, void* out, long long n, int kind, void* s) {
     if (n <= 0) return 0;
-    if (kind < 0 || kind > 2) return MRS_BAD_ARGUMENT;
+    if (kind < 0 || kind > 4) return MRS_BAD_ARGUMENT;
     const int threads = 256;
     const long long cap = 16LL * mrs_sm_count();
     if (is_bf16 && n % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
@@ -171,6 +193,21 @@ MRS_EXPORT int mrs_activation(int is_bf16, const void* in, void* out, long long 
         MRS_LAUNCH(activation_kernel<bf16>, (unsigned)blocks, threads, 0, s, (const bf16*)in, (bf16*)out, n, kind);
     else
         MRS_LAUNCH(activation_kernel<float>, (unsigned)blocks, threads, 0, s, (const float*)in, (float*)out, n, kind);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+MRS_EXPORT int mrs_gated_activation(int is_bf16, const void* gate_up, void* out, int tokens, int inter, int kind, int block, void* s) {
+    if (tokens <= 0 || inter <= 0) return 0;
+    if (kind < 0 || kind > 4 || block < 0 || (block > 0 && inter % block)) return MRS_BAD_ARGUMENT;
+    const int threads = 128;
+    const unsigned across = (unsigned)((inter + 2 * threads - 1) / (2 * threads));
+    long long down = ((long long)mrs_sm_count() * 32 + across - 1) / across;
+    if (down > tokens) down = tokens;
+    if (down > 65535) down = 65535;
+    if (is_bf16)
+        MRS_LAUNCH(gated_activation_kernel<bf16>, dim3(across, (unsigned)down), threads, 0, s, (const bf16*)gate_up, (bf16*)out, tokens, inter, kind, block);
+    else
+        MRS_LAUNCH(gated_activation_kernel<float>, dim3(across, (unsigned)down), threads, 0, s, (const float*)gate_up, (float*)out, tokens, inter, kind, block);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

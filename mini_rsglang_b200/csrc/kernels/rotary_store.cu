@@ -1,0 +1,106 @@
+// After a fused q | k (| v) (| gate ...) projection with float32 sums: the heads of q and k are rotated by their
+// token's position and pass an RMS norm, before or after the rotation; q leaves in the engine's dtype, k goes into
+// the key pages, v into the value pages.  What may vary:
+//   * rotation: the first `rot` elements of a head turn, pair i being (i, i + rot / 2) or (2 i, 2 i + 1); the
+//     pair (u, v) becomes (u cos a - v sin a, v cos a + u sin a), a = position * f_i; cosines and sines come from
+//     the step's table [tokens, rot / 2, 2] (float32); rot = 0: no rotation;
+//   * the norm x / sqrt(mean(x^2) + eps) over the whole head, with a weight of the head's size (one for all query
+//     heads, one for all key heads) or without one; before the rotation, after it, or not at all;
+//   * the values: columns of their own, or the key heads as they were projected (before norm and rotation).
+// Columns behind q, k and v (gates) are left to whoever reads them.  Key pages [pages, nkv, page, d], value pages
+// [pages, nkv, page, e]; slot < 0 writes nothing.  One warp a head; the head waits in shared memory as float32.
+#include "common.cuh"
+
+#define ROTARY_MAX_D 256
+#define ROTARY_WARPS 8
+
+namespace {
+
+__device__ __forceinline__ void head_norm(float* x, int d, const float* w, float eps, int lane) {
+    float sum = 0.0f;
+    for (int i = lane; i < d; i += 32) sum += x[i] * x[i];
+    const float scale = 1.0f / sqrtf(warp_sum(sum) / (float)d + eps);
+    for (int i = lane; i < d; i += 32) x[i] = w ? x[i] * scale * w[i] : x[i] * scale;
+    __syncwarp();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(32 * ROTARY_WARPS)
+qkv_rotary_store_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ q_norm,
+                        const float* __restrict__ k_norm, int norm_mode, float eps, const float* __restrict__ rotations, int rot,
+                        int interleaved, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                        const int* __restrict__ slots, int nq, int nkv, int d, int e, int page_size, int values_from_keys) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float heads[ROTARY_WARPS][ROTARY_MAX_D];
+    const size_t t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qw = nq * d, kw = nkv * d;
+    const float* row = proj + t * proj_stride;
+    const int slot = slots ? slots[t] : -1;
+    const bool store = slot >= 0 && k_cache != nullptr;
+    const int page = store ? slot / page_size : 0, in_page = store ? slot % page_size : 0;
+    const int half = rot / 2;
+    const float* turn = rotations ? rotations + t * (size_t)half * 2 : nullptr;
+    const int units = nq + nkv + (values_from_keys ? 0 : nkv);
+    for (int unit = warp; unit < units; unit += ROTARY_WARPS) {
+        if (unit >= nq + nkv) {                              // a value head with columns of its own
+            if (!store || !v_cache) continue;
+            const int head = unit - nq - nkv;
+            const float* src = row + qw + kw + head * e;
+            T* dst = v_cache + (((size_t)page * nkv + head) * page_size + in_page) * e;
+            for (int x = lane; x < e; x += 32) dst[x] = from_float<T>(src[x]);
+            continue;
+        }
+        const bool is_q = unit < nq;
+        const int head = is_q ? unit : unit - nq;
+        if (!is_q && !store) continue;
+        const float* src = row + (is_q ? head * d : qw + head * d);
+        float* x = heads[warp];
+        for (int i = lane; i < d; i += 32) x[i] = src[i];
+        if (!is_q && values_from_keys && v_cache) {          // the value is the key as projected
+            T* dst = v_cache + (((size_t)page * nkv + head) * page_size + in_page) * d;
+            for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(src[i]);
+        }
+        __syncwarp();
+        const float* w = is_q ? q_norm : k_norm;
+        if (norm_mode == 1) head_norm(x, d, w, eps, lane);
+        if (turn) {
+            for (int i = lane; i < half; i += 32) {
+                const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+                const float c = turn[2 * i], s = turn[2 * i + 1];
+                const float u = x[a], v = x[b];
+                x[a] = u * c - v * s;
+                x[b] = v * c + u * s;
+            }
+            __syncwarp();
+        }
+        if (norm_mode == 2) head_norm(x, d, w, eps, lane);
+        T* dst = is_q ? q_out + t * qw + (size_t)head * d : k_cache + (((size_t)page * nkv + head) * page_size + in_page) * d;
+        for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(x[i]);
+        __syncwarp();
+    }
+}
+
+}  // namespace
+
+MRS_EXPORT int mrs_qkv_rotary_store(int is_bf16, const float* proj, int proj_stride, const float* q_norm, const float* k_norm,
+                                    int norm_mode, float eps, const float* rotations, int rot, int interleaved, void* q_out,
+                                    void* k_cache, void* v_cache, const int* slots, int tokens, int nq, int nkv, int d, int e,
+                                    int page_size, int values_from_keys, void* s) {
+    if (tokens <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || d <= 0 || d > ROTARY_MAX_D || e <= 0 || page_size <= 0 || norm_mode < 0 || norm_mode > 2 || rot < 0 ||
+        rot > d || rot % 2 || (rot > 0 && !rotations) || (values_from_keys && e != d) ||
+        proj_stride < nq * d + nkv * d + (values_from_keys ? 0 : nkv * e))
+        return MRS_BAD_ARGUMENT;
+    if (rot == 0) rotations = nullptr;
+    if (is_bf16)
+        MRS_LAUNCH(qkv_rotary_store_kernel<bf16>, tokens, 32 * ROTARY_WARPS, 0, s, proj, proj_stride, q_norm, k_norm, norm_mode, eps,
+                   rotations, rot, interleaved, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, slots, nq, nkv, d, e, page_size,
+                   values_from_keys);
+    else
+        MRS_LAUNCH(qkv_rotary_store_kernel<float>, tokens, 32 * ROTARY_WARPS, 0, s, proj, proj_stride, q_norm, k_norm, norm_mode, eps,
+                   rotations, rot, interleaved, (float*)q_out, (float*)k_cache, (float*)v_cache, slots, nq, nkv, d, e, page_size,
+                   values_from_keys);
+    MRS_RETURN_LAUNCH_STATUS();
+}

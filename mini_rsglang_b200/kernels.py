@@ -848,7 +848,7 @@ GEMM_GATED_MEASURE = "MRS_GEMM_GATED_ROWS_MIN" not in os.environ                
 _gated_rows_choice: dict[tuple, bool] = {}
 
 
-def gemm_gated_rows_wins(x: torch.Tensor, weight: torch.Tensor) -> bool:
+def gemm_gated_rows_wins(x: torch.Tensor, weight: torch.Tensor, gate: str = "silu") -> bool:
     """Whether the tcgen05 gate/up product with the activation in it is the faster way for these sizes on this
     device: at least GEMM_GATED_ROWS_MIN rows, and ahead of the library's product followed by `silu_mul` when the
     two were timed (three runs each after one, CUDA events, on buffers of their own; never while a step is being
@@ -859,17 +859,20 @@ def gemm_gated_rows_wins(x: torch.Tensor, weight: torch.Tensor) -> bool:
     if not GEMM_GATED_MEASURE:
         return True
     n, k = weight.shape
-    key = (x.device, n, k, 1 << (rows - 1).bit_length() if rows <= 1024 else 1024 * min(-(-rows // 1024), 16))
+    key = (x.device, n, k, gate, 1 << (rows - 1).bit_length() if rows <= 1024 else 1024 * min(-(-rows // 1024), 16))
     if torch.cuda.is_current_stream_capturing():         # a step being recorded ran once just before: the choice is made
         return _gated_rows_choice.get(key, False)
     if key not in _gated_rows_choice:
         act = torch.empty((rows, n // 2), dtype=torch.bfloat16, device=x.device)
 
         def own():
-            gemm_gated_rows(x, weight, act)
+            gemm_gated_rows(x, weight, act, gate)
 
         def library():
-            silu_mul(torch.mm(x, weight.t()), act, 64)
+            if gate == "silu":
+                silu_mul(torch.mm(x, weight.t()), act, 64)
+            else:
+                gated_activation(torch.mm(x, weight.t()), act, gate, 64)
 
         times = []
         for run in (own, library):
@@ -893,7 +896,7 @@ def gemm_many_rows_library() -> ctypes.CDLL:
         lib = specialised_kernel_library("gemm_many_rows.cu", {})
         lib.mrs_gemm_many_rows_map.argtypes = [_c_vp, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_vp]
         lib.mrs_gemm_many_rows_map.restype = _c_int
-        lib.mrs_gemm_gated_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp]
+        lib.mrs_gemm_gated_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp]
         lib.mrs_gemm_gated_rows.restype = _c_int
         lib.mrs_gemm_act_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp]
         lib.mrs_gemm_act_rows.restype = _c_int
@@ -929,9 +932,14 @@ def gemm_gated_rows_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def gemm_gated_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-    """out[T, N / 2] = silu(x . gate^T) * (x . up^T) in bfloat16 for any number of rows; `weight` [N, K] holds, in
-    every block of 128 rows, 64 gate rows and then the 64 matching up rows (as the gated `gemm_tc`)."""
+GATE_ACTIVATIONS = ("silu", "relu")       # what the tcgen05 gate/up product applies to the gate in its epilogue
+
+
+def gemm_gated_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: str = "silu") -> None:
+    """out[T, N / 2] = act(x . gate^T) * (x . up^T) in bfloat16 for any number of rows, act "silu" or "relu"; `weight`
+    [N, K] holds, in every block of 128 rows, 64 gate rows and then the 64 matching up rows (as the gated `gemm_tc`)."""
+    if gate not in GATE_ACTIVATIONS:
+        raise InvalidRequest(f"the gated product applies one of {GATE_ACTIVATIONS} to the gate, not {gate!r}")
     global launch_count
     t, k = x.shape
     n = weight.shape[0]
@@ -943,7 +951,7 @@ def gemm_gated_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) ->
     lib = gemm_many_rows_library()
     x_keep, x_map, w_map = _many_rows_maps_of(lib, x, weight)
     launch_count += 1
-    code = lib.mrs_gemm_gated_rows(x_map, w_map, out.data_ptr(), t, n, k, sm_count(x.device), _stream())
+    code = lib.mrs_gemm_gated_rows(x_map, w_map, out.data_ptr(), t, n, k, ACTIVATIONS[gate], sm_count(x.device), _stream())
     del x_keep
     if code != 0:
         raise BackendError(f"gemm_gated_rows: {lib.mrs_gemm_many_rows_error_string(code).decode()} (code {code})")
@@ -1087,7 +1095,7 @@ def check_device_errors(certain: bool = False) -> None:
 # ------------------------------------------------------------------------------------------------
 _c_ll = ctypes.c_longlong
 _HYBRID_SIGNATURES = {
-    "mrs_postnorm_add_norm": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_float, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_postnorm_add_norm": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_float, _c_vp, _c_int, _c_int, _c_float, _c_vp],
     "mrs_glu_clamped": [_c_int, _c_vp, _c_vp, _c_int, _c_int, _c_float, _c_float, _c_vp],
     "mrs_qkv_bias_store": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int,
                            _c_int, _c_int, _c_float, _c_int, _c_vp, _c_vp, _c_float, _c_vp],
@@ -1117,8 +1125,8 @@ def hybrid_library() -> ctypes.CDLL:
 
 
 def postnorm_add_norm(stream: torch.Tensor, branch: torch.Tensor, post_weight: torch.Tensor, post_eps: float,
-                      next_weight: torch.Tensor | None, next_eps: float, out: torch.Tensor | None) -> None:
-    """stream += rmsnorm(branch) * post_weight; with `next_weight`, out = rmsnorm(stream) * next_weight.
+                      next_weight: torch.Tensor | None, next_eps: float, out: torch.Tensor | None, mult: float = 1.0) -> None:
+    """stream += mult * rmsnorm(branch) * post_weight; with `next_weight`, out = rmsnorm(stream) * next_weight.
     `branch` holds a product's float32 sums; the norms and the sum are float32."""
     rows, width = stream.shape
     _need(stream, torch.float32, "postnorm stream")
@@ -1129,7 +1137,7 @@ def postnorm_add_norm(stream: torch.Tensor, branch: torch.Tensor, post_weight: t
         _need(out, None, "postnorm out", (rows, width))
     _check(hybrid_library().mrs_postnorm_add_norm(_is_bf16(out.dtype) if out is not None else 0, stream.data_ptr(),
                                                   branch.data_ptr(), post_weight.data_ptr(), _ptr(next_weight), float(post_eps),
-                                                  float(next_eps), _ptr(out), rows, width, _stream()), "postnorm_add_norm")
+                                                  float(next_eps), _ptr(out), rows, width, float(mult), _stream()), "postnorm_add_norm")
 
 
 def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
@@ -1426,12 +1434,13 @@ _LATENT_SIGNATURES = {
     "mrs_scale": [_c_vp, ctypes.c_longlong, _c_float, _c_vp],
 }
 _EXPERT_SIGNATURES = {
-    "mrs_moe_route": [_c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_vp],
+    "mrs_moe_route": [_c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_vp],
     "mrs_moe_align": [_c_vp, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_vp],
-    "mrs_moe_product_simt": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
-    "mrs_moe_product_rows": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_product_simt": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_product_rows": [_c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
     "mrs_moe_gather_rows": [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
-    "mrs_moe_product_mma": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_gather_scaled_rows": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_product_mma": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
     "mrs_moe_combine": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
 }
 _latent_lib = None
@@ -1569,11 +1578,12 @@ def sigmoid_gate_mul(x: torch.Tensor, gate: torch.Tensor) -> None:
 
 
 def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, chosen: torch.Tensor, weights: torch.Tensor,
-              shared_gate: torch.Tensor | None, experts: int, top: int, scale: float, sigmoid_scores: bool = False) -> None:
+              shared_gate: torch.Tensor | None, experts: int, top: int, scale: float, sigmoid_scores: bool = False,
+              normalize: bool = True) -> None:
     """Router logits float32 [tokens, experts (+ 1) or more] -> `chosen` [tokens, top] int32, the `top` experts with the
     largest score + correction, and `weights` [tokens, top] float32, score / (sum of the chosen + 1e-20) * scale; scores
     are the softmax (or the sigmoids) of the first `experts` columns.  With `shared_gate` [tokens] the column after them
-    is one more gate, whose sigmoid it gets.  Further columns are not read."""
+    is one more gate, whose sigmoid it gets.  Further columns are not read.  `normalize` False: the weights are score * scale."""
     tokens = logits.shape[0]
     _need(logits, torch.float32, "router logits")
     if logits.dim() != 2 or logits.shape[1] < experts + (1 if shared_gate is not None else 0):
@@ -1586,7 +1596,7 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, chosen: tor
         _need(shared_gate, torch.float32, "shared gate", (tokens,))
     _check(expert_library().mrs_moe_route(logits.data_ptr(), logits.shape[1], _ptr(correction), chosen.data_ptr(), weights.data_ptr(),
                                           _ptr(shared_gate), tokens, experts, top, float(scale), int(sigmoid_scores),
-                                          int(shared_gate is not None), _stream()), "moe_route")
+                                          int(shared_gate is not None), int(normalize), _stream()), "moe_route")
 
 
 def moe_capacity(pairs: int, routed: int, tile: int) -> int:
@@ -1629,37 +1639,41 @@ def moe_align(chosen: torch.Tensor, routed: int, tile: int, sorted_rows: torch.T
 
 
 def moe_product(x: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-                top: int, gated: bool, kernel: str = "simt", block: int = 0) -> None:
+                top: int, gated: bool, kernel: str = "simt", block: int = 0, activation: str | None = None) -> None:
     """One product of the experts over the lists of `moe_align`: `kernel` "simt" (CUDA cores, tiles of `moe_simt_tile()`
     rows, every size), "rows" (CUDA cores, few rows an expert: tiles of `moe_rows_tile()` rows, the weights streamed once;
     rows of a multiple of 16 bytes) or "mma" (mma.sync, bfloat16, k a multiple of 8, tiles of `moe_mma_tile()` rows).
     `gated`: x [tokens, k], weight [experts, 2 n, k] (all gate rows, then all up rows; with `block`, blocks of that many
     gate rows each followed by the matching up rows), out [capacity, n] = silu(gate) * up of every listed pair's token;
-    else x [capacity, k], weight [experts, n, k], out [pairs, n] written at the pair."""
+    else x [capacity, k], weight [experts, n, k], out [pairs, n] written at the pair; or, with `activation` (one of
+    ACTIVATIONS; not gated), out [capacity, n] = activation(sums), written at the rows' places in the lists."""
     capacity = sorted_rows.shape[0]
+    if activation is not None and (gated or activation not in ACTIVATIONS):
+        raise InvalidRequest(f"moe_product: an activation {sorted(ACTIVATIONS)} goes with the ungated product only")
+    act = ACTIVATIONS[activation] if activation is not None else -1
     k = x.shape[1]
     n = out.shape[1]
     _need(x, None, "expert input")
     _need(weight, x.dtype, "expert weights", (weight.shape[0], (2 if gated else 1) * n, k))
     _need(out, x.dtype, "expert output")
-    if (out.shape[0] if gated else x.shape[0]) != capacity:
+    if (out.shape[0] if gated else x.shape[0]) != capacity or (act >= 0 and out.shape[0] != capacity):
         raise InvalidRequest("moe_product: the listed rows do not match the lists")
     if kernel == "mma":
         _need(x, torch.bfloat16, "expert input")
         _check(expert_library().mrs_moe_product_mma(int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
                                                     weight.data_ptr(), out.data_ptr(), capacity, n, k, top, int(block) if gated else 0,
-                                                    _stream()), "moe_product_mma")
+                                                    act, _stream()), "moe_product_mma")
         return
     if kernel == "rows":
         _check(expert_library().mrs_moe_product_rows(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(),
                                                      tile_expert.data_ptr(), weight.data_ptr(), out.data_ptr(), capacity, n, k, top,
-                                                     int(block) if gated else 0, _stream()), "moe_product_rows")
+                                                     int(block) if gated else 0, act, _stream()), "moe_product_rows")
         return
     if kernel != "simt":
         raise InvalidRequest(f"moe_product: unknown kernel {kernel!r}")
     _check(expert_library().mrs_moe_product_simt(_is_bf16(x.dtype), int(gated), x.data_ptr(), sorted_rows.data_ptr(), tile_expert.data_ptr(),
                                                  weight.data_ptr(), out.data_ptr(), capacity, n, k, top, int(block) if gated else 0,
-                                                 _stream()), "moe_product_simt")
+                                                 act, _stream()), "moe_product_simt")
 
 
 MOE_TC_BLOCK = 64              # gate rows of a block in the layout of the product for many rows; the 64 matching up rows follow
@@ -1677,7 +1691,7 @@ def moe_tc_library() -> ctypes.CDLL:
         lib = specialised_kernel_library("experts_tc.cu", {})
         lib.mrs_moe_tc_map.argtypes = [_c_vp, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_vp]
         lib.mrs_moe_tc_map.restype = _c_int
-        lib.mrs_moe_product_tc.argtypes = [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp]
+        lib.mrs_moe_product_tc.argtypes = [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp]
         lib.mrs_moe_product_tc.restype = _c_int
         lib.mrs_moe_tc_tile.argtypes = []
         lib.mrs_moe_tc_tile.restype = _c_int
@@ -1711,11 +1725,14 @@ def _moe_tc_map(lib, t: torch.Tensor, rows: int, cols: int, box_rows: int, keep:
 
 
 def moe_product_tc(x_rows: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-                   gated: bool) -> None:
+                   gated: bool, activation: str | None = None) -> None:
     """One product of the experts on the tcgen05 tensor cores over lists in tiles of 128 rows.  `x_rows` [capacity, k]: the
     rows in the order of the lists.  `gated`: weight [experts, 2 n, k] in blocks of 64 gate and 64 up rows, out
-    [capacity, n] = silu(gate) * up; else weight [experts, n, k], out [pairs, n] written at the rows' pairs."""
+    [capacity, n] = silu(gate) * up; else weight [experts, n, k], out [pairs, n] written at the rows' pairs, or with
+    `activation` (one of ACTIVATIONS) out [capacity, n] = activation(sums) at the rows' places."""
     global launch_count
+    if activation is not None and (gated or activation not in ACTIVATIONS):
+        raise InvalidRequest(f"moe_product_tc: an activation {sorted(ACTIVATIONS)} goes with the ungated product only")
     capacity, k = x_rows.shape
     experts, rows_each = weight.shape[0], weight.shape[1]
     _need(x_rows, torch.bfloat16, "expert rows")
@@ -1728,7 +1745,7 @@ def moe_product_tc(x_rows: torch.Tensor, sorted_rows: torch.Tensor, tile_expert:
     _, w_map = _moe_tc_map(lib, weight, experts * rows_each, k, 256, keep=True)
     launch_count += 1
     code = lib.mrs_moe_product_tc(int(gated), x_map, w_map, tile_expert.data_ptr(), sorted_rows.data_ptr(), out.data_ptr(), capacity,
-                                  rows_each, k, sm_count(x_rows.device), _stream())
+                                  rows_each, k, ACTIVATIONS[activation] if activation is not None else -1, sm_count(x_rows.device), _stream())
     del x_keep
     if code != 0:
         raise BackendError(f"moe_product_tc: {lib.mrs_moe_tc_error_string(code).decode()} (code {code})")
@@ -1740,6 +1757,59 @@ def moe_gather_rows(x: torch.Tensor, sorted_rows: torch.Tensor, out: torch.Tenso
     _need(out, torch.bfloat16, "gathered rows", (sorted_rows.shape[0], x.shape[1]))
     _check(expert_library().mrs_moe_gather_rows(x.data_ptr(), sorted_rows.data_ptr(), out.data_ptr(), out.shape[0], x.shape[1], top,
                                                 _stream()), "moe_gather_rows")
+
+
+def moe_gather_scaled_rows(x: torch.Tensor, sorted_rows: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, top: int) -> None:
+    """out[place] = x[pair / top] * weights[pair] for every listed pair (float32 product, rounded once), zeros where a run
+    is filled up; `weights` float32 [tokens, top]."""
+    _need(x, None, "expert input")
+    _need(out, x.dtype, "gathered rows", (sorted_rows.shape[0], x.shape[1]))
+    _need(weights, torch.float32, "expert weights")
+    _check(expert_library().mrs_moe_gather_scaled_rows(_is_bf16(x.dtype), x.data_ptr(), sorted_rows.data_ptr(), weights.data_ptr(),
+                                                       out.data_ptr(), out.shape[0], x.shape[1], top, _stream()), "moe_gather_scaled_rows")
+
+
+def moe_plain_experts(h: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor | None, up: torch.Tensor, down: torch.Tensor,
+                      y: torch.Tensor, routed: int, activation: str, kernel: str | None = None) -> None:
+    """Experts without a gate: y[token * top + choice] = W_down[e] act(W_up[e] x) with x = h[token] (* weights[token, choice]
+    when `weights` are given: the weight multiplies what the expert reads) for every pair whose expert is one of the first
+    `routed`.  `up` [routed, inner, width], `down` [routed, width, inner].  The listed pairs' rows are gathered (and
+    weighted) first; the up product writes act(sums) at the rows' places, the down product at the pairs.  `kernel` as
+    `moe_experts` (None: by the number of pairs)."""
+    tokens, top = chosen.shape
+    inner = down.shape[2]
+    if kernel is None:
+        if tokens * top <= MOE_ROWS_MAX_PAIRS and moe_rows_supported(h, inner):
+            kernel = "rows"
+        elif tokens * top >= MOE_TC_MIN_PAIRS and moe_plain_tc_supported(h, up, down):
+            kernel = "tc"
+        else:
+            kernel = "mma" if moe_mma_supported(h, inner) else ("rows" if moe_rows_supported(h, inner) and tokens * top <= 4 * MOE_ROWS_MAX_PAIRS else "simt")
+    tile = {"tc": 128, "mma": moe_mma_tile(), "simt": moe_simt_tile(), "rows": moe_rows_tile()}[kernel]
+    capacity = moe_capacity(tokens * top, routed, tile)
+    sorted_rows = torch.empty((capacity,), dtype=torch.int32, device=h.device)
+    tile_expert = torch.empty((capacity // tile + 1,), dtype=torch.int32, device=h.device)
+    moe_align(chosen, routed, tile, sorted_rows, tile_expert)
+    rows = torch.empty((capacity, h.shape[1]), dtype=h.dtype, device=h.device)
+    if weights is not None:
+        moe_gather_scaled_rows(h, sorted_rows, weights, rows, top)
+    elif h.dtype is torch.bfloat16 and h.shape[1] % 8 == 0:
+        moe_gather_rows(h, sorted_rows, rows, top)
+    else:
+        moe_gather_scaled_rows(h, sorted_rows, torch.ones((tokens, top), dtype=torch.float32, device=h.device), rows, top)
+    act = torch.empty((capacity, inner), dtype=h.dtype, device=h.device)
+    if kernel == "tc":
+        moe_product_tc(rows, sorted_rows, tile_expert, up, act, gated=False, activation=activation)
+        moe_product_tc(act, sorted_rows, tile_expert, down, y, gated=False)
+        return
+    moe_product(rows, sorted_rows, tile_expert, up, act, top, gated=False, kernel=kernel, activation=activation)
+    moe_product(act, sorted_rows, tile_expert, down, y, top, gated=False, kernel=kernel)
+
+
+def moe_plain_tc_supported(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> bool:
+    """bfloat16, a width and an inner size of a multiple of 8, weights on 16-byte boundaries."""
+    return (x.dtype is torch.bfloat16 and x.shape[1] % 8 == 0 and down.shape[2] % 8 == 0 and up.data_ptr() % 16 == 0
+            and down.data_ptr() % 16 == 0)
 
 
 def moe_experts(h: torch.Tensor, chosen: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, y: torch.Tensor, routed: int,
@@ -1778,10 +1848,11 @@ def moe_experts(h: torch.Tensor, chosen: torch.Tensor, gate_up: torch.Tensor, do
     moe_product(act, sorted_rows, tile_expert, down, y, top, gated=False, kernel=kernel)
 
 
-def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tensor | None, chosen: torch.Tensor, weights: torch.Tensor,
-                shared_gate: torch.Tensor | None, out: torch.Tensor, routed: int) -> None:
+def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tensor | None, chosen: torch.Tensor,
+                weights: torch.Tensor | None, shared_gate: torch.Tensor | None, out: torch.Tensor, routed: int) -> None:
     """out[token] = sum over its choices of weight * (y[pair] for one of the first `routed` experts, else h[token])
-    (+ shared_gate[token] * shared_out[token])."""
+    (+ shared_gate[token] * shared_out[token]).  `weights` None: every weight is 1 (they were applied to the experts' inputs);
+    `shared_gate` None: the shared expert's output counts fully."""
     tokens, width = h.shape
     top = chosen.shape[1]
     _need(h, None, "expert input", (tokens, width))
@@ -1791,11 +1862,13 @@ def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tenso
         raise InvalidRequest("moe_combine: experts with weights need their outputs")
     _need(out, h.dtype, "combined output", (tokens, width))
     _need(chosen, torch.int32, "chosen experts", (tokens, top))
-    _need(weights, torch.float32, "expert weights", (tokens, top))
+    if weights is not None:
+        _need(weights, torch.float32, "expert weights", (tokens, top))
     if shared_out is not None:
         _need(shared_out, h.dtype, "shared expert output", (tokens, width))
-        _need(shared_gate, torch.float32, "shared gate", (tokens,))
-    _check(expert_library().mrs_moe_combine(_is_bf16(h.dtype), _ptr(y), h.data_ptr(), _ptr(shared_out), chosen.data_ptr(), weights.data_ptr(),
+        if shared_gate is not None:
+            _need(shared_gate, torch.float32, "shared gate", (tokens,))
+    _check(expert_library().mrs_moe_combine(_is_bf16(h.dtype), _ptr(y), h.data_ptr(), _ptr(shared_out), chosen.data_ptr(), _ptr(weights),
                                             _ptr(shared_gate), out.data_ptr(), tokens, width, top, routed, _stream()), "moe_combine")
 
 
@@ -1806,6 +1879,7 @@ _PARALLEL_SIGNATURES = {
     "mrs_add_branches_norm": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_vp],
     "mrs_activation": [_c_int, _c_vp, _c_vp, ctypes.c_longlong, _c_int, _c_vp],
     "mrs_scale_softcap": [_c_vp, ctypes.c_longlong, _c_float, _c_float, _c_vp],
+    "mrs_gated_activation": [_c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
 }
 _DELTA_SIGNATURES = {
     "mrs_delta_prepare": [_c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
@@ -1816,7 +1890,7 @@ _DELTA_SIGNATURES = {
 }
 _parallel_lib = None
 _delta_lib = None
-ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"gelu_erf": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "relu2": 4}      # relu2: the square of relu
 
 
 def parallel_library() -> ctypes.CDLL:
@@ -1868,6 +1942,20 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
     _need(out, x.dtype, "activation output", tuple(x.shape))
     _check(parallel_library().mrs_activation(_is_bf16(x.dtype), x.data_ptr(), out.data_ptr(), x.numel(), ACTIVATIONS[kind], _stream()),
            "activation")
+
+
+def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, kind: str, block: int = 0) -> None:
+    """out = act(gate) * up (float32 arithmetic), act one of ACTIVATIONS.  `gate_up` holds all gate columns and then all up
+    columns (block 0), or alternating blocks of `block` gate columns and the `block` matching up columns."""
+    if kind not in ACTIVATIONS:
+        raise InvalidRequest(f"activation {kind!r} is not built; known: {sorted(ACTIVATIONS)}")
+    tokens, inter = out.shape
+    _need(gate_up, out.dtype, "gate_up", (tokens, 2 * inter))
+    _need(out, None, "gated activation out")
+    if block and inter % block:
+        raise InvalidRequest("gated_activation: the inner size is no multiple of the block")
+    _check(parallel_library().mrs_gated_activation(_is_bf16(out.dtype), gate_up.data_ptr(), out.data_ptr(), tokens, inter,
+                                                   ACTIVATIONS[kind], int(block), _stream()), "gated_activation")
 
 
 def scale_softcap_(x: torch.Tensor, scale: float, cap: float) -> None:
@@ -1927,3 +2015,103 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, ep
     _need(out, None, "head norm out", (tokens, inner))
     _check(delta_library().mrs_head_norm_gate(_is_bf16(out.dtype), o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(),
                                               float(eps), out.data_ptr(), tokens, heads, e, _stream()), "head_norm_gate")
+
+
+# ------------------------------------------------------------------------------------------------
+# rotated and normed heads with values of their own or taken from the keys; embeddings with a table of token pairs;
+# a stream joined with another
+# ------------------------------------------------------------------------------------------------
+_ROTARY_SIGNATURES = {
+    "mrs_qkv_rotary_store": [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_float, _c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp,
+                             _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_embed_pairs": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_float, _c_int,
+                        _c_ll, _c_ll, _c_int, _c_vp],
+    "mrs_concat_rows": [_c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp],
+}
+_rotary_lib = None
+HEAD_NORM_PLACES = {None: 0, "before_rotation": 1, "after_rotation": 2}
+ROTARY_MAX_HEAD = 256
+
+
+def rotary_library() -> ctypes.CDLL:
+    global _rotary_lib
+    if _rotary_lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        from .csrc.build import rotary_kernel_library
+
+        _rotary_lib = _typed(rotary_kernel_library(), _ROTARY_SIGNATURES)
+    return _rotary_lib
+
+
+def qkv_rotary_store(proj: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
+                     slots: torch.Tensor | None, nq: int, nkv: int, d: int, e: int, rotations: torch.Tensor | None = None,
+                     rotary_dim: int = 0, pairing: str = "split_half", norm_place: str | None = None, q_norm: torch.Tensor | None = None,
+                     k_norm: torch.Tensor | None = None, norm_eps: float = 0.0, values_from_keys: bool = False) -> None:
+    """After a fused projection whose float32 rows start with q | k (| v): the first `rotary_dim` elements of every query and
+    key head turn by the token's position (`rotations` [tokens, rotary_dim / 2, 2] float32 cosines and sines; `pairing`
+    "split_half": element i with i + rotary_dim / 2, "interleaved": 2 i with 2 i + 1), the heads pass an RMS norm over all
+    their elements `norm_place` the rotation ("before_rotation", "after_rotation", None: no norm) with `q_norm` / `k_norm`
+    [d] float32 or, where one is None, without a weight; q goes to `q_out`, k into the key pages [pages, nkv, page, d], v
+    into the value pages [pages, nkv, page, e] at `slots`.  `values_from_keys`: the rows have no value columns, a value is
+    its key head as projected (e = d).  Columns behind these are not read."""
+    tokens = proj.shape[0]
+    need = nq * d + nkv * d + (0 if values_from_keys else nkv * e)
+    _need(proj, torch.float32, "projection")
+    if proj.dim() != 2 or proj.shape[1] < need:
+        raise InvalidRequest("qkv_rotary_store: the projection's rows are shorter than q, k and v")
+    if norm_place not in HEAD_NORM_PLACES:
+        raise InvalidRequest(f"qkv_rotary_store: a head norm stands {sorted(k for k in HEAD_NORM_PLACES if k)} or nowhere")
+    if pairing not in ("split_half", "interleaved"):
+        raise InvalidRequest(f"qkv_rotary_store: unknown pairing {pairing!r}")
+    if d > ROTARY_MAX_HEAD or rotary_dim > d or rotary_dim % 2 or (values_from_keys and e != d):
+        raise InvalidRequest("qkv_rotary_store: heads of up to 256 elements, an even rotated part, values from keys of equal size")
+    _need(q_out, None, "q_out", (tokens, nq * d))
+    page_size = 1
+    if k_cache is not None:
+        page_size = k_cache.shape[2]
+        _need(k_cache, q_out.dtype, "key pages")
+        _need(v_cache, q_out.dtype, "value pages")
+        if tuple(k_cache.shape[1:]) != (nkv, page_size, d) or tuple(v_cache.shape[1:]) != (nkv, page_size, e):
+            raise InvalidRequest("qkv_rotary_store: the pages do not match heads, page size and head sizes")
+        _need(slots, torch.int32, "slots", (tokens,))
+    if rotary_dim:
+        _need(rotations, torch.float32, "rotations", (tokens, rotary_dim // 2, 2))
+    for w in (q_norm, k_norm):
+        if w is not None:
+            _need(w, torch.float32, "head norm weight", (d,))
+    _check(rotary_library().mrs_qkv_rotary_store(
+        _is_bf16(q_out.dtype), proj.data_ptr(), proj.shape[1], _ptr(q_norm), _ptr(k_norm), HEAD_NORM_PLACES[norm_place], float(norm_eps),
+        _ptr(rotations) if rotary_dim else None, int(rotary_dim), int(pairing == "interleaved"), q_out.data_ptr(), _ptr(k_cache),
+        _ptr(v_cache), _ptr(slots) if k_cache is not None else None, tokens, nq, nkv, d, e, page_size, int(values_from_keys), _stream()),
+        "qkv_rotary_store")
+
+
+def embed_pairs(table: torch.Tensor, pair_table: torch.Tensor, ctx, last_token: torch.Tensor, stream: torch.Tensor, scale: float,
+                buckets: int, mul_prev: int, mul_cur: int, write_state: bool = True) -> None:
+    """stream[t] = table[id] * scale + pair_table[(previous id * mul_prev + id * mul_cur) mod buckets], the table's row
+    number `buckets` for a sequence's first token.  The token before a portion's first one is `last_token[slot]` (int32
+    [slots]) of the sequence's state slot, which then gets the portion's last token unless `write_state` is False.  `ctx`
+    gives the step's ids, positions, sequences, first rows and state slots."""
+    tokens, width = stream.shape
+    vocab = table.shape[0]
+    _need(table, None, "embedding table", (vocab, width))
+    _need(pair_table, table.dtype, "pair table", (buckets + 1, width))
+    _need(stream, torch.float32, "stream")
+    _need(last_token, torch.int32, "last tokens")
+    _need(ctx.token_ids, torch.int32, "ids", (tokens,))
+    _check(rotary_library().mrs_embed_pairs(_is_bf16(table.dtype), table.data_ptr(), pair_table.data_ptr(), ctx.token_ids.data_ptr(),
+                                            ctx.positions.data_ptr(), ctx.seq_of_token.data_ptr(), ctx.q_start.data_ptr(),
+                                            ctx.state_slots.data_ptr(), last_token.data_ptr(), stream.data_ptr(), tokens, width, vocab,
+                                            float(scale), int(buckets), int(mul_prev), int(mul_cur), int(write_state), _stream()),
+           "embed_pairs")
+
+
+def concat_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t] ; b[t]] in out's dtype; a and b float32 [rows, width]."""
+    rows, width = a.shape
+    _need(a, torch.float32, "first rows")
+    _need(b, torch.float32, "second rows", (rows, width))
+    _need(out, None, "joined rows", (rows, 2 * width))
+    _check(rotary_library().mrs_concat_rows(_is_bf16(out.dtype), a.data_ptr(), b.data_ptr(), out.data_ptr(), rows, width, _stream()),
+           "concat_rows")

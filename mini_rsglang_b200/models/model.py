@@ -20,7 +20,8 @@ class Model:
         self.spec = spec
         self.runtime = runtime
         self.embedding, self.blocks, self.final_norm, self.head = spec.build_parts()
-        for part in (self.embedding, *self.blocks, self.final_norm, self.head):
+        self.stream_entries = spec.build_stream_entries()
+        for part in (self.embedding, *self.stream_entries, *self.blocks, self.final_norm, self.head):
             part.bind(tensors, runtime)
         self.final_norm.gathers_rows = True
         # cache entry that each run of the order reads; runs that borrow a cache write nothing
@@ -37,6 +38,11 @@ class Model:
 
     def state_needs(self):
         return [self._need(e, "state_need") for e in self.spec.run_order]
+
+    def embedding_state_need(self):
+        """What the embedding keeps of a request between steps (a `StateNeed`), or None."""
+        need = getattr(self.embedding, "state_need", None)
+        return need() if need is not None else None
 
     def replayable(self) -> bool:
         """Whether steps of single decoded tokens may be recorded: every part that keeps a cache allows it."""
@@ -56,7 +62,7 @@ class Model:
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
-        for part in (self.embedding, *self.blocks, self.final_norm, self.head):
+        for part in (self.embedding, *self.stream_entries, *self.blocks, self.final_norm, self.head):
             for t in _tensors_of(part):
                 if t.data_ptr() not in seen:
                     seen.add(t.data_ptr())
@@ -68,17 +74,30 @@ class Model:
         when no logits are wanted (the head is then skipped, as in the reference,
         crates/engine/src/lib.rs:132-135)."""
         ctx.shared.clear()           # a context may be run again (a recorded step): nothing of the run before is kept
-        stream = self.embedding.forward(ctx)
+        if storage.embedding_state is not None:
+            stream = self.embedding.forward(ctx, storage.embedding_state)
+        else:
+            stream = self.embedding.forward(ctx)
         if ctx.observe:
             ctx.observe("embedding", stream)
         pending = None
         order = self.spec.run_order
+        # a stream entry reads the embedding's output; the stream itself is updated in place, so a copy is kept
+        origin = stream.clone() if any(e.enter is not None for e in order) else None
         for index, entry in enumerate(order):
             block = self.blocks[entry.layer]
             ctx.label = f"layer{index}"
+            if entry.enter is not None:
+                delta = plain_or_none(pending)          # the block before was told of no following norm: the stream holds its sum
+                if delta is not None:
+                    stream.add_(delta.float())
+                stream, pending = self.stream_entries[entry.enter].forward(stream, origin, ctx), None
             extra = {}
-            if block.links_norms:        # the norm that reads the stream after this block
-                extra["next_norm"] = self.blocks[order[index + 1].layer].entry_norm if index + 1 < len(order) else self.final_norm
+            if block.links_norms:        # the norm that reads the stream after this block; none when something stands between
+                if index + 1 < len(order):
+                    extra["next_norm"] = self.blocks[order[index + 1].layer].entry_norm if order[index + 1].enter is None else None
+                else:
+                    extra["next_norm"] = self.final_norm
             pending = block.forward(stream, pending, ctx, storage.entries[self.cache_entry[index]],
                                     self.writes_cache[index] and not ctx.rehearsal, **extra)
         if ctx.observe:              # the reference norms every row before it gathers the wanted ones (qwen3.rs:228-233)

@@ -8,8 +8,9 @@ import os
 from dataclasses import dataclass
 from typing import Callable
 
-from ..config.model_config import ModelConfig, NiduvikConfig, NubipelConfig, Qwen3Config, SatedraConfig
+from ..config.model_config import MigenexConfig, ModelConfig, NiduvikConfig, NubipelConfig, Qwen3Config, SatedraConfig
 from ..errors import InvalidRequest
+from .migenex import migenex_spec
 from .niduvik import niduvik_spec
 from .nubipel import nubipel_spec
 from .qwen3 import qwen3_spec
@@ -37,6 +38,7 @@ register_architecture("qwen3", Qwen3Config, qwen3_spec)
 register_architecture("niduvik", NiduvikConfig, niduvik_spec)
 register_architecture("satedra", SatedraConfig, satedra_spec)
 register_architecture("nubipel", NubipelConfig, nubipel_spec)
+register_architecture("migenex", MigenexConfig, migenex_spec)
 
 
 def config_from_dict(raw: dict) -> ModelConfig:

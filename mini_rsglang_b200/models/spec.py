@@ -5,7 +5,7 @@ from dataclasses import dataclass, field
 from typing import Mapping
 
 from ..errors import InvalidRequest
-from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, PartSpec
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, STREAM_ENTRIES, PartSpec
 from ..weights.spec import WeightSpec
 
 
@@ -13,12 +13,13 @@ from ..weights.spec import WeightSpec
 class LayerSpec:
     """One layer: the arrangement (`block`, a registered block kind) and a part for every role that this
     kind arranges.  `prefix` is the root of the layer's tensor names; a part's own root hangs below it
-    under `names[role]` (the role itself when `names` does not give one)."""
+    under `names[role]` (the role itself when `names` does not give one).  `params`: parameters of the arrangement itself."""
 
     prefix: str
     block: str
     parts: Mapping[str, PartSpec]
     names: Mapping[str, str] = field(default_factory=dict)
+    params: Mapping[str, object] = field(default_factory=dict)
 
 
 def pre_norm_layer(prefix: str, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, feed_forward: PartSpec,
@@ -32,10 +33,12 @@ def pre_norm_layer(prefix: str, norm1: PartSpec, mixer: PartSpec, norm2: PartSpe
 @dataclass(frozen=True)
 class RunEntry:
     """One run of a layer.  `cache_of` names an earlier entry of the run order whose cache this
-    run reads instead of keeping one of its own (it then writes nothing)."""
+    run reads instead of keeping one of its own (it then writes nothing).  `enter` names one of the model's stream
+    entries (`ModelSpec.stream_entries`), which acts on the residual stream right before this run."""
 
     layer: int
     cache_of: int | None = None
+    enter: int | None = None
 
 
 @dataclass
@@ -51,6 +54,7 @@ class ModelSpec:
     head_prefix: str
     run_order: list[RunEntry] = field(default_factory=list)
     ignorable_weights: tuple[str, ...] = ()
+    stream_entries: list[tuple[PartSpec, str]] = field(default_factory=list)     # (part, root of its tensor names)
 
     def __post_init__(self):
         if not self.run_order:
@@ -58,6 +62,8 @@ class ModelSpec:
         for index, entry in enumerate(self.run_order):
             if not 0 <= entry.layer < len(self.layers):
                 raise InvalidRequest(f"run order names layer {entry.layer}, the model has {len(self.layers)}")
+            if entry.enter is not None and not 0 <= entry.enter < len(self.stream_entries):
+                raise InvalidRequest(f"run order names stream entry {entry.enter}, the model has {len(self.stream_entries)}")
             if entry.cache_of is not None:
                 if not 0 <= entry.cache_of < index or self.run_order[entry.cache_of].cache_of is not None:
                     raise InvalidRequest("cache_of must name an earlier run that keeps a cache of its own")
@@ -75,14 +81,19 @@ class ModelSpec:
                                      f"missing {missing}, unknown {unknown}")
             parts = {role: registry.build(layer.parts[role], f"{layer.prefix}.{layer.names.get(role, role)}")
                      for role, registry in kind.roles.items() if role in layer.parts}
-            blocks.append(kind(prefix=layer.prefix, **parts))
+            blocks.append(kind(prefix=layer.prefix, **layer.params, **parts))
         final_norm = NORMS.build(self.final_norm, self.final_norm_prefix)
         head = HEADS.build(self.head, self.head_prefix)
         return embedding, blocks, final_norm, head
 
+    def build_stream_entries(self):
+        return [STREAM_ENTRIES.build(part, prefix) for part, prefix in self.stream_entries]
+
     def weight_specs(self) -> list[WeightSpec]:
         embedding, blocks, final_norm, head = self.build_parts()
         specs = embedding.weight_specs()
+        for entry in self.build_stream_entries():
+            specs += entry.weight_specs()
         for block in blocks:
             specs += block.weight_specs()
         return specs + final_norm.weight_specs() + head.weight_specs()

@@ -1,4 +1,4 @@
-"""Grouped-query attention without rotation, with what some designs put around its scores and values:
+"""Grouped-query attention with what some designs put around its scores and values:
 
   * biases on the q, k and v projections;
   * key heads of `head_dim` and value heads of `value_dim` elements;
@@ -7,12 +7,16 @@
     evenly in the logarithm of the distance up to `bias_far`, the last row for everything beyond;
   * a sliding window that also keeps the first `keep_first` positions in sight (at their true distances); or sight in
     chunks: position i sees j <= i only where floor(i / chunk) = floor(j / chunk), chunks counted from position 0;
-  * an RMS norm over every query and key head (one weight of the head's size for all query heads, one for all key heads);
+  * an RMS norm over every query and key head (one weight of the head's size for all query heads, one for all key heads,
+    or no weight);
+  * a rotation of query and key heads by their positions (any registered position encoding: all or part of a head, split
+    halves or interleaved pairs), with the head norm before or after it;
+  * values that are the key heads as projected (before norm and rotation): no value projection;
   * a softmax with a sink: one more term in the denominator that has no key and no value, exp(0) or exp of a learned
     number a head (not scaled);
   * values blended with those of the first layer that blends, (1 - m) v + m v_first per token; the blended values
     are what the cache holds;
-  * an output gate, one sigmoid a (token, head), from the same input as the projections.
+  * an output gate from the same input as the projections: one sigmoid a (token, head), or one a (token, value element).
 
 One projection gives q | k | v | gate (float32 sums), one kernel adds the biases, blends, gates and writes the
 pages, one kernel attends.  Every constant is a parameter; none of the extras is tied to another."""
@@ -26,7 +30,7 @@ from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
 from .attention import attention_tile_lists, choose_splits, plan_attention_tiles
-from .base import MIXERS, KVNeed, Mixer, StepFacts
+from .base import MIXERS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, StepFacts
 from .linear import linear
 
 
@@ -59,8 +63,13 @@ class BiasedWindowAttention(Mixer):
                  bias_rows: int = 0, bias_far: float = 0.0, sink: bool = False, projection_bias: bool = False,
                  value_mix: str | None = None, value_mix_source: bool = False, output_gate: bool = False,
                  chunk: int = 0, sink_logits: bool = False, head_norm_eps: float | None = None,
-                 names: dict | None = None):
-        """`chunk` > 0 (no window then): sight within the query's chunk of positions.  `sink_logits`: the sink's logit is a
+                 position: PartSpec | None = None, head_norm_place: str = "before_rotation", head_norm_weights: bool = True,
+                 values_from_keys: bool = False, names: dict | None = None):
+        """`position`: a position encoding that rotates query and key heads (None: none); `head_norm_place`: the head norm
+        stands "before_rotation" or "after_rotation"; `head_norm_weights` False: it has no weights.  `values_from_keys`: no
+        value projection, a value head is its key head as projected (`value_dim` = `head_dim`).  `output_gate`: True or
+        "heads": one gate a (token, head); "elements": one a value element of every head.
+        `chunk` > 0 (no window then): sight within the query's chunk of positions.  `sink_logits`: the sink's logit is a
         learned number a query head.  `head_norm_eps`: query and key heads pass an RMS norm with this epsilon (None: no norm).
         `value_mix`: a key under which the layers that blend values find the first one's values within a step
         (None: no blending); `value_mix_source`: this layer is that first one (its own mixing weight is unused).
@@ -87,7 +96,25 @@ class BiasedWindowAttention(Mixer):
         # bias_rows -1: as many rows as the checkpoint's table has
         if self.bias_rows > 0:
             self._check_bias_table(self.bias_rows)
-        self.projection_bias, self.output_gate = bool(projection_bias), bool(output_gate)
+        self.projection_bias = bool(projection_bias)
+        self.output_gate = "heads" if output_gate is True else (output_gate or None)
+        if self.output_gate not in (None, "heads", "elements"):
+            raise InvalidRequest(f"{prefix}: an output gate is one a head ('heads') or one a value element ('elements')")
+        self.position = POSITION_ENCODINGS.build(position, prefix) if position is not None else None
+        self.head_norm_place, self.head_norm_weights = head_norm_place, bool(head_norm_weights)
+        self.values_from_keys = bool(values_from_keys)
+        if head_norm_place not in ("before_rotation", "after_rotation"):
+            raise InvalidRequest(f"{prefix}: a head norm stands before_rotation or after_rotation")
+        if self.values_from_keys and self.e != self.d:
+            raise InvalidRequest(f"{prefix}: values taken from the keys have the keys' size")
+        # what only the kernel with rotations does, and what only the one with biases and blending does
+        self.rotary_store = (self.position is not None or self.values_from_keys or not self.head_norm_weights
+                             or head_norm_place == "after_rotation" or self.output_gate == "elements")
+        if self.rotary_store and (projection_bias or value_mix or self.output_gate == "heads"):
+            raise InvalidRequest(f"{prefix}: rotation, values from keys, weightless or late head norms and gates a value element "
+                                 "are not built together with projection biases, blended values or gates a head")
+        if self.rotary_store and self.d > kernels.ROTARY_MAX_HEAD:
+            raise InvalidRequest(f"{prefix}: rotated heads have at most {kernels.ROTARY_MAX_HEAD} elements")
         self.value_mix, self.value_mix_source = value_mix, bool(value_mix_source)
         self.leaf = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "bias_table": "distance_bias",
@@ -105,9 +132,10 @@ class BiasedWindowAttention(Mixer):
     def weight_specs(self):
         n = self.leaf
         specs = [WeightSpec(self.name(n["q"]), (self.nq * self.d, self.width)),
-                 WeightSpec(self.name(n["k"]), (self.nkv * self.d, self.width)),
-                 WeightSpec(self.name(n["v"]), (self.nkv * self.e, self.width)),
-                 WeightSpec(self.name(n["o"]), (self.width, self.nq * self.e))]
+                 WeightSpec(self.name(n["k"]), (self.nkv * self.d, self.width))]
+        if not self.values_from_keys:
+            specs.append(WeightSpec(self.name(n["v"]), (self.nkv * self.e, self.width)))
+        specs.append(WeightSpec(self.name(n["o"]), (self.width, self.nq * self.e)))
         if self.projection_bias:
             specs += [WeightSpec(self.name(n["q_bias"]), (self.nq * self.d,), "bias"),
                       WeightSpec(self.name(n["k_bias"]), (self.nkv * self.d,), "bias"),
@@ -117,8 +145,8 @@ class BiasedWindowAttention(Mixer):
         if self.value_mix:
             specs.append(WeightSpec(self.name(n["mix"]), (), "bias"))
         if self.output_gate:
-            specs.append(WeightSpec(self.name(n["gate"]), (self.nq, self.width)))
-        if self.head_norm_eps is not None:
+            specs.append(WeightSpec(self.name(n["gate"]), (self.nq * (self.e if self.output_gate == "elements" else 1), self.width)))
+        if self.head_norm_eps is not None and self.head_norm_weights:
             specs += [WeightSpec(self.name(n["q_norm"]), (self.d,), "vector"), WeightSpec(self.name(n["k_norm"]), (self.d,), "vector")]
         if self.sink_logits:
             specs.append(WeightSpec(self.name(n["sink"]), (self.nq,), "bias"))
@@ -136,7 +164,9 @@ class BiasedWindowAttention(Mixer):
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
         n = self.leaf
-        rows = [tensors[self.name(n[k])] for k in ("q", "k", "v")]
+        rows = [tensors[self.name(n[k])] for k in (("q", "k") if self.values_from_keys else ("q", "k", "v"))]
+        if self.position is not None:
+            self.position.bind(tensors, runtime)
         if self.output_gate:
             rows.append(tensors[self.name(n["gate"])])
         self.fused = torch.cat(rows, dim=0).contiguous()
@@ -150,7 +180,7 @@ class BiasedWindowAttention(Mixer):
             self.distance_bias = table[rows_of].contiguous()         # [distances, heads]: the table, a row a distance
         if self.value_mix and not self.value_mix_source:
             self.mix = float(tensors[self.name(n["mix"])].float().item())
-        if self.head_norm_eps is not None:
+        if self.head_norm_eps is not None and self.head_norm_weights:
             self.q_norm = tensors[self.name(n["q_norm"])].float().contiguous()
             self.k_norm = tensors[self.name(n["k_norm"])].float().contiguous()
         if self.sink_logits:
@@ -161,8 +191,23 @@ class BiasedWindowAttention(Mixer):
         device, dtype = self.o.device, self.runtime.dtype
         proj = linear(h, self.fused, out_dtype=torch.float32)
         q = torch.empty((tokens, self.nq * self.d), dtype=dtype, device=device)
-        gate = torch.empty((tokens, self.nq), dtype=torch.float32, device=device) if self.output_gate else None
+        gate = torch.empty((tokens, self.nq), dtype=torch.float32, device=device) if self.output_gate == "heads" else None
         v_first, mode = None, 0
+        if self.rotary_store:
+            rotation = self.position.rotation() if self.position is not None else None
+            if rotation is not None and rotation.rotary_dim == 0:
+                rotation = None
+            if rotation is not None and rotation.magnitude != 1.0:
+                raise InvalidRequest(f"{self.prefix}: stretched cosines and sines are not built for this attention")
+            kernels.qkv_rotary_store(proj, q, cache.k if write_cache else None, cache.v if write_cache else None,
+                                     ctx.slots[cache.group] if write_cache else None, self.nq, self.nkv, self.d, self.e,
+                                     rotations=self.position.rotations(ctx) if rotation is not None else None,
+                                     rotary_dim=rotation.rotary_dim if rotation is not None else 0,
+                                     pairing=rotation.pairing if rotation is not None else "split_half",
+                                     norm_place=self.head_norm_place if self.head_norm_eps is not None else None,
+                                     q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.head_norm_eps or 0.0,
+                                     values_from_keys=self.values_from_keys)
+            return self._attend(q, proj, gate, ctx, cache)
         if self.value_mix:
             key = ("value_mix", self.value_mix)
             if self.value_mix_source:
@@ -176,6 +221,12 @@ class BiasedWindowAttention(Mixer):
                                ctx.slots[cache.group] if write_cache else None, self.nq, self.nkv, self.d, self.e,
                                v_first=v_first, mix_mode=mode, mix=self.mix, gate_out=gate, q_norm=self.q_norm, k_norm=self.k_norm,
                                norm_eps=self.head_norm_eps or 0.0)
+        return self._attend(q, proj, gate, ctx, cache)
+
+    def _attend(self, q, proj, gate, ctx, cache):
+        """The attention over the pages and the output projection; `gate`: the heads' gates, if there are such."""
+        tokens = q.shape[0]
+        device, dtype = self.o.device, self.runtime.dtype
         out = torch.empty((tokens, self.nq * self.e), dtype=dtype, device=device)
         table = ctx.block_tables[cache.group]
         arguments = self._tile_plan()
@@ -196,6 +247,8 @@ class BiasedWindowAttention(Mixer):
                     kernels.attention_biased_mma(q, cache.k, cache.v, ctx.positions, table, tiles, out, self.nq, self.nkv, self.d,
                                                  self.e, self.scale, self.softcap, self.window, self.keep_first, self.distance_bias,
                                                  gate, self.sink, narrow=is_narrow, splits=splits, sink_logits=self.sinks, chunk=self.chunk)
+        if self.output_gate == "elements":         # the gates are the projection's last columns, still float32 sums
+            kernels.sigmoid_gate_mul(out, proj[:, proj.shape[1] - self.nq * self.e:])
         return linear(out, self.o, out_dtype=torch.float32)
 
     def _tile_plan(self) -> tuple:

@@ -15,6 +15,8 @@ Interfaces (all tensors on the device; `ctx` is an `engine.context.StepContext`)
       residual float32 [T, width] (+ delta of the engine's dtype), normalised; the sum is
       written back unless told otherwise; `rows` picks source rows
   Embedding.forward(ctx) -> stream                 float32 [T, width] from `ctx.token_ids`
+  StreamEntry.forward(stream, origin, ctx) -> stream   before a run of a layer: the stream it reads, from the stream so far
+      and the embedding's output
   Head.forward(hidden) -> logits                   float32 [rows, vocab]; `hidden` may be a `Prenormed`
   PositionEncoding.rotation() -> Rotation | None   how the mixer's kernel rotates: frequencies, how many of the
       head's elements turn, which elements pair, a factor on cosines and sines; None: no rotation
@@ -225,9 +227,21 @@ class Norm(Part):
 
 
 class Embedding(Part):
-    """Token ids -> the float32 residual stream."""
+    """Token ids -> the float32 residual stream.  An embedding that keeps something of a request between steps (the last
+    token it brought) says so with `state_need`; its `forward` is then given `state`, the array [slots, *shape]."""
+
+    def state_need(self) -> "StateNeed | None":
+        return None
 
     def forward(self, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class StreamEntry(Part):
+    """What stands before a run of a layer and acts on the whole residual stream: `forward(stream, origin, ctx)` returns the
+    stream that the layer reads (float32 [T, width]); `origin` is the stream as the embedding left it."""
+
+    def forward(self, stream: torch.Tensor, origin: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -346,6 +360,7 @@ class Registry:
 
 
 EMBEDDINGS = Registry("embedding")
+STREAM_ENTRIES = Registry("stream entry")
 HEADS = Registry("output head")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")

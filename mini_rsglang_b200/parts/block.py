@@ -63,8 +63,8 @@ class PreNormBlock(Block):
 
 @BLOCKS.register("sandwich_norm")
 class SandwichNormBlock(Block):
-    """A norm before and a norm after each branch: x <- x + norm1b(mixer(norm1(x))), then, where the layer has a
-    feed-forward, x <- x + norm2b(feed_forward(norm2(x))).
+    """A norm before and a norm after each branch: x <- x + m norm1b(mixer(norm1(x))), then, where the layer has a
+    feed-forward, x <- x + m norm2b(feed_forward(norm2(x))); m = `branch_scale` (1 unless the layer's spec says otherwise).
 
     The branches' last products leave float32 sums; one kernel norms a branch's output, adds it to the float32
     stream and runs the norm that reads the stream next (`kernels.postnorm_add_norm`), so the sum and both
@@ -76,8 +76,9 @@ class SandwichNormBlock(Block):
     optional_roles = ("norm2", "feed_forward", "norm2b")
     entry_role = "norm1"
 
-    def __init__(self, prefix: str, **parts):
+    def __init__(self, prefix: str, branch_scale: float = 1.0, **parts):
         super().__init__(prefix, **parts)
+        self.branch_scale = float(branch_scale)
         given = [self.parts.get(role) is not None for role in self.optional_roles]
         if any(given) and not all(given):
             raise InvalidRequest(f"block at {prefix!r}: a feed-forward comes with the norm before and the norm after it")
@@ -87,13 +88,13 @@ class SandwichNormBlock(Block):
                 raise InvalidRequest(f"block at {prefix!r}: the norm {role!r} must be an RMS norm with float32 weights")
 
     def _join(self, stream, branch, post, following):
-        """stream += post(branch); the rows of `following` (a norm, or None) over the sum."""
+        """stream += branch_scale * post(branch); the rows of `following` (a norm, or None) over the sum."""
         fused = following is not None and getattr(following, "rides_on_products", False) and not following.gathers_rows
         if branch.dtype is not torch.float32:          # a branch written for another arrangement
             branch = branch.float()
         out = torch.empty(stream.shape, dtype=self.runtime.dtype, device=stream.device) if fused else None
         kernels.postnorm_add_norm(stream, branch, post.weight, post.eps, following.weight if fused else None,
-                                  following.eps if fused else 0.0, out)
+                                  following.eps if fused else 0.0, out, self.branch_scale)
         return Normed(out, following, stream) if fused else None
 
     def forward(self, stream, pending, ctx, cache, write_cache=True, next_norm=None):

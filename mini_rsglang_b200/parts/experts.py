@@ -6,6 +6,10 @@ their outputs (no biases anywhere).
   weight_e = s_e / (sum of the chosen s + 1e-20) * scale
   out = sum over the chosen of weight_e * expert_e(h),   expert_e(h) = W_down silu(W_gate h) * (W_up h)
 
+Variations, all parameters: `normalize` False leaves the weights as the chosen scores (times scale); `form` "plain" makes
+an expert W_down act(W_up h) without a gate, `activation` one of `kernels.ACTIVATIONS`; `weight_on` "input" multiplies what
+a chosen expert reads by its weight instead of what it returns: out = sum over the chosen of expert_e(weight_e * h).
+
 The last `identity` experts of the router have no tensors: their output is their input.  A shared expert (any
 registered feed-forward) may run for every token beside them, behind one sigmoid gate a token.
 
@@ -28,6 +32,7 @@ from .linear import linear
 class RoutedExperts(FeedForward):
     def __init__(self, prefix: str, width: int, experts: int, top: int, inner: int, identity: int = 0, scale: float = 1.0,
                  score: str = "softmax", correction: bool = False, shared: PartSpec | None = None, shared_gate: bool = False,
+                 normalize: bool = True, form: str = "gated", activation: str = "silu", weight_on: str = "output",
                  names: dict | None = None):
         """`experts` with tensors, then `identity` without; `shared`: the feed-forward that every token passes as well
         (its root is the leaf "shared" below this part's), `shared_gate`: behind a sigmoid gate of one number a token.
@@ -42,6 +47,15 @@ class RoutedExperts(FeedForward):
         if score not in ("softmax", "sigmoid"):
             raise InvalidRequest(f"{prefix}: router scores {score!r} are not built; softmax or sigmoid")
         self.score, self.correction = score, bool(correction)
+        self.normalize, self.form, self.activation, self.weight_on = bool(normalize), form, activation, weight_on
+        if form not in ("gated", "plain") or weight_on not in ("output", "input"):
+            raise InvalidRequest(f"{prefix}: experts are 'gated' or 'plain', their weights on the 'output' or the 'input'")
+        if form == "gated" and activation != "silu":
+            raise InvalidRequest(f"{prefix}: gated experts with {activation!r} are not built; only silu")
+        if form == "plain" and activation not in kernels.ACTIVATIONS:
+            raise InvalidRequest(f"{prefix}: activation {activation!r} is not built; known: {sorted(kernels.ACTIVATIONS)}")
+        if weight_on == "input" and (form != "plain" or self.identity):
+            raise InvalidRequest(f"{prefix}: weights on the experts' input are built for plain experts without identity experts")
         self.leaf = {"router": "router.weight", "correction": "router.correction", "expert": "experts.{}", "gate": "gate_proj.weight",
                      "up": "up_proj.weight", "down": "down_proj.weight", "shared": "shared", "shared_gate": "shared_gate.weight"}
         self.leaf.update(names or {})
@@ -61,8 +75,9 @@ class RoutedExperts(FeedForward):
         n = self.leaf
         specs = []
         for number in range(self.experts):
-            specs += [WeightSpec(self._expert(number, "gate"), (self.inner, self.width)),
-                      WeightSpec(self._expert(number, "up"), (self.inner, self.width)),
+            if self.form == "gated":
+                specs.append(WeightSpec(self._expert(number, "gate"), (self.inner, self.width)))
+            specs += [WeightSpec(self._expert(number, "up"), (self.inner, self.width)),
                       WeightSpec(self._expert(number, "down"), (self.width, self.inner))]
         specs.append(WeightSpec(self.name(n["router"]), (self.all_experts, self.width)))
         if self.correction:
@@ -79,7 +94,10 @@ class RoutedExperts(FeedForward):
         # When serving in bfloat16 and the inner size allows it, blocks of 64 gate rows alternate with the 64 matching up
         # rows: a weight tile of the product for many rows then holds both factors of its outputs.
         self.block = kernels.MOE_TC_BLOCK if runtime.is_bf16 and self.experts and self.inner % kernels.MOE_TC_BLOCK == 0 else 0
-        if self.experts and self.block:
+        if self.experts and self.form == "plain":
+            self.block = 0
+            self.gate_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.experts)]).contiguous()      # [experts, inner, width]
+        elif self.experts and self.block:
             b = self.block
             self.gate_up = torch.stack([torch.stack([tensors[self._expert(e, "gate")].view(-1, b, self.width),
                                                      tensors[self._expert(e, "up")].view(-1, b, self.width)], dim=1)
@@ -111,16 +129,16 @@ class RoutedExperts(FeedForward):
         weights = torch.empty((tokens, self.top), dtype=torch.float32, device=device)
         shared_gate = torch.empty((tokens,), dtype=torch.float32, device=device) if self.shared_gate else None
         kernels.moe_route(logits, self.correction_values, chosen, weights, shared_gate, self.all_experts, self.top, self.scale,
-                          sigmoid_scores=self.score == "sigmoid")
+                          sigmoid_scores=self.score == "sigmoid", normalize=self.normalize)
+        on_input = self.weight_on == "input"
         y = None
         if self.experts:
             y = torch.empty((tokens * self.top, self.width), dtype=dtype, device=device)
-            kernels.moe_experts(h, chosen, self.gate_up, self.down, y, self.experts, block=self.block)
-        shared_out = None
-        if self.shared is not None:
-            shared_out = self.shared.forward(h, ctx)
-            if self.shared_gate is False:            # no gate: the shared expert counts fully
-                shared_gate = torch.ones((tokens,), dtype=torch.float32, device=device)
+            if self.form == "plain":
+                kernels.moe_plain_experts(h, chosen, weights if on_input else None, self.gate_up, self.down, y, self.experts, self.activation)
+            else:
+                kernels.moe_experts(h, chosen, self.gate_up, self.down, y, self.experts, block=self.block)
+        shared_out = self.shared.forward(h, ctx) if self.shared is not None else None       # no gate: it counts fully
         out = torch.empty((tokens, self.width), dtype=dtype, device=device)
-        kernels.moe_combine(y, h, shared_out, chosen, weights, shared_gate, out, self.experts)
+        kernels.moe_combine(y, h, shared_out, chosen, None if on_input else weights, shared_gate, out, self.experts)
         return out

@@ -1,5 +1,6 @@
-"""Rotary position encoding, split-half pairing (j, j + d/2), every dimension rotary
-(reference: crates/kernels/src/ops.cu:79-90).  The part owns the table of inverse
+"""Rotary position encoding: split-half pairing (j, j + d/2) with every dimension rotary
+(reference: crates/kernels/src/ops.cu:79-90) unless a part of the head (`rotary_dim`) or pairs of neighbours
+(`pairing="interleaved"`) are asked for.  The part owns the table of inverse
 frequencies; angle = position * f_j, its cosine and sine and the rotation are float32.  The
 cosines and sines of a step's tokens are computed once and shared by every layer that rotates
 by the same frequencies (`rotations`); kernels that have the angles at hand compute them
@@ -17,9 +18,15 @@ from .base import POSITION_ENCODINGS, PositionEncoding, Rotation
 
 @POSITION_ENCODINGS.register("rope")
 class RotaryPosition(PositionEncoding):
-    def __init__(self, prefix: str, head_dim: int, theta: float):
+    def __init__(self, prefix: str, head_dim: int, theta: float, rotary_dim: int | None = None, pairing: str = "split_half"):
+        """`rotary_dim`: the first so many elements of a head turn (None: all), pair j by position * theta^(-2j / rotary_dim);
+        `pairing`: "split_half" (j with j + rotary_dim / 2) or "interleaved" (2j with 2j + 1)."""
         super().__init__(prefix)
         self.head_dim, self.theta = int(head_dim), float(theta)
+        self.rotary_dim = self.head_dim if rotary_dim is None else int(rotary_dim)
+        self.pairing = pairing
+        if pairing not in ("split_half", "interleaved") or self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
+            raise InvalidRequest("rotary positions: an even number of a head's elements turn, in split halves or interleaved pairs")
         self.inv_freq: torch.Tensor | None = None
         self.shared_key = None
 
@@ -33,15 +40,15 @@ class RotaryPosition(PositionEncoding):
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        frequencies = self.inverse_frequencies(self.head_dim, self.theta)
+        frequencies = self.inverse_frequencies(self.rotary_dim, self.theta)
         self.inv_freq = frequencies.to(runtime.device)
         self.shared_key = ("rotations", frequencies.numpy().tobytes())     # layers with the same frequencies share a step's table
 
     def rotation(self):
-        return Rotation(self.inv_freq, self.head_dim, "split_half", 1.0)
+        return Rotation(self.inv_freq, self.rotary_dim, self.pairing, 1.0)
 
     def rotations(self, ctx):
-        """[tokens, head_dim / 2, 2] float32 (cos, sin) for the step's positions; kept in `ctx.shared` for the
+        """[tokens, rotary_dim / 2, 2] float32 (cos, sin) for the step's positions; kept in `ctx.shared` for the
         step's other layers (the model empties it when a step begins)."""
         shared = getattr(ctx, "shared", None)
         if shared is not None and self.shared_key in shared:
