@@ -276,11 +276,34 @@ def parallel_configs(size: dict, vocab: int = 32768):
     return nubipel, hybrid_configs(size, vocab)[0]
 
 
+def looped_configs(size: dict, vocab: int = 32768):
+    """Migenex at these layer sizes: six layers of which the third and fourth are passed twice (eight layer runs), layers with
+    values taken from the keys (heads of 128, a window of 1,024, every value element gated) and a relu-gated feed-forward
+    taking turns with layers that see everything (heads of 128, scores capped at 30) and route 4 of 32 ungated experts of
+    ff / 8 beside a shared one of ff / 4; a table of 65,536 token pairs.  Beside it Satedra, the engine's other model of
+    windowed attention with routed and shared experts, at equal width, heads, experts and depth."""
+    w, ff = size["width"], size["ff"]
+    rot = {"base": 1000000.0, "dims": 128}
+    keyed = {"type": "attention_2", "mlp": {"kind": "dense", "ff": ff},
+             "mixer": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+                       "rot": rot}}
+    routed = {"type": "attention", "mlp": {"kind": "moe", "expert": {"ff": ff // 8}, "shared": {"ff": ff // 4}, "router": {"experts": 32, "top": 4}},
+              "mixer": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+                        "rot": rot}}
+    runs = size["layers"]
+    layers = [keyed if i % 2 == 0 else routed for i in range(runs - 2)]
+    migenex = {"architecture": "Migenex", "vocab": vocab, "width": w, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+               "embedding": {"scale": 1.0, "bigram": {"buckets": 65536, "mul_prev": 1000003, "mul_cur": 31}},
+               "loop": {"start": 2, "stop": 4, "times": 2}, "layers": layers}
+    return migenex, latent_configs(size, vocab)[0]
+
+
 # design: (title, what stands beside it, the key of that model in the output, the two configurations)
 DESIGNS = {"niduvik": ("Niduvik", "Qwen3 of equal width, heads, feed-forward and depth", "qwen3", hybrid_configs),
            "satedra": ("Satedra", "Qwen3 of equal width, heads and depth, its feed-forward as wide as the experts a token passes", "qwen3",
                        latent_configs),
-           "nubipel": ("Nubipel", "Niduvik of equal width, heads, feed-forward and depth", "niduvik", parallel_configs)}
+           "nubipel": ("Nubipel", "Niduvik of equal width, heads, feed-forward and depth", "niduvik", parallel_configs),
+           "migenex": ("Migenex", "Satedra of equal width, heads, experts and depth", "satedra", looped_configs)}
 
 
 def hybrid_run(args, torch, peak: dict) -> dict:

@@ -361,6 +361,28 @@ template <> struct Store16<bf16> {
     }
 };
 
+// The weighted gather with sixteen bytes a thread and step: k a multiple of 16 bytes, x and out on 16-byte boundaries.
+template <typename T>
+__global__ void moe_gather_scaled_rows_vec_kernel(const T* __restrict__ x, const int* __restrict__ sorted_rows, const float* __restrict__ weights,
+                                                  T* __restrict__ out, int k, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int V = Piece<T>::N;
+    const int pair = sorted_rows[blockIdx.x];
+    const T* src = x + (size_t)(pair < 0 ? 0 : pair / top) * k;
+    const float w = pair >= 0 ? weights[pair] : 0.0f;
+    T* dst = out + (size_t)blockIdx.x * k;
+    for (int i = threadIdx.x * V; i < k; i += blockDim.x * V) {
+        float v[V] = {};
+        if (pair >= 0) {
+            Piece<T>::load(src + i, v);
+#pragma unroll
+            for (int e = 0; e < V; ++e) v[e] *= w;
+        }
+        Store16<T>::store(dst + i, v);
+    }
+}
+
 template <typename T>
 __global__ void moe_combine_vec_kernel(const T* __restrict__ y, const T* __restrict__ h, const T* __restrict__ shared_out,
                                        const int* __restrict__ chosen, const float* __restrict__ weights, const float* __restrict__ shared_gate,
@@ -488,6 +510,13 @@ MRS_EXPORT int mrs_moe_gather_scaled_rows(int is_bf16, const void* x, const int*
                                           int k, int top, void* stream) {
     if (capacity <= 0) return 0;
     if (k <= 0 || top <= 0 || !weights) return MRS_BAD_ARGUMENT;
+    if (k % (is_bf16 ? 8 : 4) == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        if (is_bf16)
+            MRS_LAUNCH(moe_gather_scaled_rows_vec_kernel<bf16>, capacity, 128, 0, stream, (const bf16*)x, sorted_rows, weights, (bf16*)out, k, top);
+        else
+            MRS_LAUNCH(moe_gather_scaled_rows_vec_kernel<float>, capacity, 128, 0, stream, (const float*)x, sorted_rows, weights, (float*)out, k, top);
+        MRS_RETURN_LAUNCH_STATUS();
+    }
     if (is_bf16)
         MRS_LAUNCH(moe_gather_scaled_rows_kernel<bf16>, capacity, 128, 0, stream, (const bf16*)x, sorted_rows, weights, (bf16*)out, k, top);
     else

@@ -20,22 +20,27 @@ def rms_norm(x, weight, eps):
 
 def embed(tokens, w, c):
     """embed[t] * scale + bigram[(previous * mul_prev + t * mul_cur) mod buckets]; the first token of a sequence takes
-    the table's last row (row number `buckets`)."""
-    b = c["embedding"]["bigram"]
-    x = w["embed"][tokens] * c["embedding"]["scale"]
+    the table's last row (row number `buckets`).  A model without a table of pairs adds nothing."""
+    b = c.get("embedding", {}).get("bigram")
+    x = w["embed"][tokens] * c.get("embedding", {}).get("scale", 1.0)
+    if b is None:
+        return x
     rows = []
     for i, t in enumerate(tokens.tolist()):
         rows.append(b["buckets"] if i == 0 else (int(tokens[i - 1]) * b["mul_prev"] + t * b["mul_cur"]) % b["buckets"])
     return x + w["bigram"][torch.tensor(rows)]
 
 
-def rotate(x, base, dims, layout):
-    """x [T, heads, d]: the first `dims` elements of every head turn by position * base^(-2i/dims); pair i is
-    (i, i + dims/2) ("half") or (2i, 2i + 1) ("interleaved"); (u, v) -> (u cos - v sin, v cos + u sin)."""
+def rotate(x, base, dims, layout, start=0):
+    """x [T, heads, d], rows at the positions start, start + 1, ...: the first `dims` elements of every head turn by
+    position * base^(-2i/dims); pair i is (i, i + dims/2) ("half") or (2i, 2i + 1) ("interleaved");
+    (u, v) -> (u cos - v sin, v cos + u sin)."""
     T = x.shape[0]
     half = dims // 2
+    if half == 0:
+        return x.clone()
     i = torch.arange(half, dtype=x.dtype)
-    angle = torch.arange(T, dtype=x.dtype)[:, None] * base ** (-2.0 * i / dims)[None, :]
+    angle = torch.arange(start, start + T, dtype=x.dtype)[:, None] * base ** (-2.0 * i / dims)[None, :]
     cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
     out = x.clone()
     if layout == "half":
