@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
     const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
     const bf16* __restrict__ q, const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
     const Tile* __restrict__ tiles, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-    int* __restrict__ counters, int nq, int nkv, int page_size, int page_shift, float scale_log2, int window, int splits,
+    int* __restrict__ counters, int nq, int nkv, int page_size, int page_shift, float scale_log2, float scale, float cap, int window, int splits,
     int in_cluster) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ int is_last;
@@ -261,7 +261,9 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
                     const int key = key0 + nt * 8 + 2 * t + (e & 1);
                     const int pos = row_pos[e >> 1];
                     const bool seen = key <= pos && key < key_end && (window <= 0 || key > pos - window);
-                    sc[nt][e] = seen ? sc[nt][e] * scale_log2 : -CUDART_INF_F;
+                    // cap > 0: the scaled score is bent into (-cap, cap) before the softmax
+                    const float bent = cap > 0.0f ? cap * tanhf(sc[nt][e] * scale / cap) * 1.4426950408889634f : sc[nt][e] * scale_log2;
+                    sc[nt][e] = seen ? bent : -CUDART_INF_F;
                     block_max[e >> 1] = fmaxf(block_max[e >> 1], sc[nt][e]);
                 }
 #pragma unroll
@@ -484,8 +486,9 @@ MRS_EXPORT long long mrs_attention_decode_tma_scratch_floats(int tiles, int nkv,
 MRS_EXPORT int mrs_attention_decode_tma(const void* k_map, const void* v_map, const void* q, const int* positions,
                                         const int* block_table, int table_width, const int* tiles, int num_tiles,
                                         void* out, float* scratch, int* counters, int nq, int nkv, int page_size,
-                                        float scale, int window, int splits, void* stream) {
+                                        float scale, int window, int splits, float cap, void* stream) {
     if (num_tiles <= 0) return 0;
+    if (cap < 0.0f) return MRS_BAD_ARGUMENT;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || page_size < 8 || nkv <= 0 || nq % nkv || nq / nkv > ROWS || splits < 1 || splits > 256)
         return MRS_BAD_ARGUMENT;
@@ -533,12 +536,12 @@ MRS_EXPORT int mrs_attention_decode_tma(const void* k_map, const void* v_map, co
         return (int)cudaLaunchKernelEx(&config, attention_decode_kernel, *reinterpret_cast<const CUtensorMap*>(k_map),
                                        *reinterpret_cast<const CUtensorMap*>(v_map), (const bf16*)q, positions, block_table, table_width,
                                        (const Tile*)tiles, (bf16*)out, part_o, part_ml, counters, nq, nkv, page_size, shift, scale_log2,
-                                       window, splits, 1);
+                                       scale, cap, window, splits, 1);
     }
     MRS_LAUNCH(attention_decode_kernel, dim3(num_tiles, nkv, splits), THREADS, SMEM_BYTES, stream,
         *reinterpret_cast<const CUtensorMap*>(k_map), *reinterpret_cast<const CUtensorMap*>(v_map), (const bf16*)q,
         positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, part_o, part_ml, counters, nq, nkv, page_size,
-        shift, scale_log2, window, splits, 0);
+        shift, scale_log2, scale, cap, window, splits, 0);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

@@ -70,6 +70,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// A soft cap on the scaled scores, in the exponent's unit: cap * tanh(x * scale / cap) * log2(e) with tanh(z) = 1 - 2 / (e^(2z) + 1);
+// `cap_in` = 2 * scale * log2(e) / cap, `cap_out` = cap * log2(e).  Two trips to the special-function unit (2^x and a
+// reciprocal, 2 ulp each); what the subtraction loses for small z is an absolute error of 2^-23 * cap, the rounding of a
+// float32 score of the cap's size.  A masked score (-inf) stays masked.
+__device__ __forceinline__ float soft_cap_log2(float x, float cap_in, float cap_out) {
+    const float e = fast_exp2(x * cap_in);
+    const float capped = fmaf(__fdividef(-2.0f, e + 1.0f), cap_out, cap_out);
+    return x == -CUDART_INF_F ? x : capped;
+}
+
 // The softmax threads are bound by the instructions they issue, so two of sm_100's wider ones are used: the
 // maximum of three numbers, and arithmetic on two floats at once (a pair of registers taken as one operand).
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -99,11 +109,13 @@ struct Barriers {
 
 constexpr size_t SMEM_BYTES = 1024 + TILES * Q_TILE_BYTES + 2 * STAGES * KV_TILE_BYTES + sizeof(Barriers) + 16;
 
+// CAPPED: the scores pass the soft cap (a variant of its own, so that the plain one keeps its registers)
+template <bool CAPPED>
 __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
     const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
     const __grid_constant__ CUtensorMap v_map, const int* __restrict__ positions, const int* __restrict__ block_table,
     int table_width, const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv, int page_size,
-    int page_shift, float scale_log2, int window, float* __restrict__ partials) {
+    int page_shift, float scale_log2, int window, float* __restrict__ partials, float cap_in, float cap_out) {
     extern __shared__ unsigned char smem_raw[];
     // the grid runs over the key/value heads first: with the entries sorted by their work, all heavy CTAs start first
     const Tile work = tiles[blockIdx.y];
@@ -348,7 +360,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
                 }
             }
             // the scale is positive, so the maximum of the scaled scores is the scaled maximum
-            const float block_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])) * scale_log2;
+            // (and the cap grows with its argument, so the maximum of the capped scores is the capped maximum)
+            const float raw_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3]));
+            const float block_max = CAPPED ? soft_cap_log2(raw_max, cap_in, cap_out) : raw_max * scale_log2;
             // the reference moves only when the maximum outgrew it by the threshold (always from -inf)
             float alpha = 1.0f;
             const bool moved = block_max > reference + RESCALE_THRESHOLD;
@@ -375,7 +389,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
                 uint32_t packed[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
-                    const float2 t = fma2(make_float2(x[c0 + c], x[c0 + c + 1]), scale2, minus_base);
+                    const float2 t = CAPPED
+                        ? make_float2(soft_cap_log2(x[c0 + c], cap_in, cap_out) - base, soft_cap_log2(x[c0 + c + 1], cap_in, cap_out) - base)
+                        : fma2(make_float2(x[c0 + c], x[c0 + c + 1]), scale2, minus_base);
                     const float2 p = make_float2(fast_exp2(t.x), fast_exp2(t.y));
                     part_sum[(c >> 1) & 3] = add2(part_sum[(c >> 1) & 3], p);
                     __nv_bfloat162 pair = __floats2bfloat162_rn(p.x, p.y);
@@ -522,23 +538,33 @@ MRS_EXPORT long long mrs_attention_prefill_tc_partial_floats(int num_tiles, int 
 MRS_EXPORT int mrs_attention_prefill_tc(const void* q_map, const void* k_map, const void* v_map, const int* positions,
                                         const int* block_table, int table_width, const int* tiles, int num_tiles,
                                         void* out, int nq, int nkv, int page_size, float scale, int window,
-                                        float* partials, int with_shares, void* stream) {
+                                        float* partials, int with_shares, float cap, void* stream) {
     if (num_tiles <= 0) return 0;
     if (with_shares && (!partials || num_tiles > 65535)) return MRS_BAD_ARGUMENT;
+    if (cap < 0.0f || !(scale > 0.0f)) return MRS_BAD_ARGUMENT;
+    // cap > 0: the scaled scores are bent into (-cap, cap), cap * tanh(score / cap), before the softmax
+    const float cap_in = cap > 0.0f ? 2.0f * scale * 1.4426950408889634f / cap : 0.0f, cap_out = cap * 1.4426950408889634f;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || page_size < 8 || nkv <= 0 || nq % nkv || nq / nkv > BM) return MRS_BAD_ARGUMENT;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     for (int done = 0; done < num_tiles; done += 65535) {         // a grid's second dimension ends at 65,535
         const int now = num_tiles - done < 65535 ? num_tiles - done : 65535;
-        MRS_LAUNCH(attention_prefill_kernel, dim3(nkv, now), THREADS, SMEM_BYTES, stream,
+        if (cap > 0.0f)
+            MRS_LAUNCH(attention_prefill_kernel<true>, dim3(nkv, now), THREADS, SMEM_BYTES, stream,
                    *reinterpret_cast<const CUtensorMap*>(q_map), *reinterpret_cast<const CUtensorMap*>(k_map),
                    *reinterpret_cast<const CUtensorMap*>(v_map), positions, block_table, table_width, (const Tile*)tiles + done,
-                   (bf16*)out, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window, with_shares ? partials : nullptr);
+                   (bf16*)out, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window, with_shares ? partials : nullptr, cap_in, cap_out);
+        else
+            MRS_LAUNCH(attention_prefill_kernel<false>, dim3(nkv, now), THREADS, SMEM_BYTES, stream,
+                   *reinterpret_cast<const CUtensorMap*>(q_map), *reinterpret_cast<const CUtensorMap*>(k_map),
+                   *reinterpret_cast<const CUtensorMap*>(v_map), positions, block_table, table_width, (const Tile*)tiles + done,
+                   (bf16*)out, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window, with_shares ? partials : nullptr, cap_in, cap_out);
     }
     if (with_shares)
         MRS_LAUNCH(attention_prefill_merge_kernel, dim3(nkv, num_tiles, TILES * BM / 8), 256, 0, stream, (const Tile*)tiles, (const float*)partials,

@@ -8,7 +8,8 @@
 //     heads, one for all key heads) or without one; before the rotation, after it, or not at all;
 //   * the values: columns of their own, or the key heads as they were projected (before norm and rotation).
 // Columns behind q, k and v (gates) are left to whoever reads them.  Key pages [pages, nkv, page, d], value pages
-// [pages, nkv, page, e]; slot < 0 writes nothing.  One warp a head; the head waits in shared memory as float32.
+// [pages, nkv, page, e]; slot < 0 writes nothing.  One warp a head; the head waits in shared memory as float32.  Heads of a
+// multiple of four elements in rows on 16-byte boundaries (VEC) come and go four elements a lane and access.
 #include "common.cuh"
 
 #define ROTARY_MAX_D 256
@@ -24,7 +25,27 @@ __device__ __forceinline__ void head_norm(float* x, int d, const float* w, float
     __syncwarp();
 }
 
-template <typename T>
+template <typename T> __device__ __forceinline__ void put4(T* p, float4 v);
+template <> __device__ __forceinline__ void put4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void put4<bf16>(bf16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// n elements from float32 `src` to `dst` of the engine's dtype, a warp together
+template <typename T, bool VEC>
+__device__ __forceinline__ void copy_out(T* dst, const float* src, int n, int lane) {
+    if (VEC) {
+        for (int i = 4 * lane; i < n; i += 128) put4<T>(dst + i, *reinterpret_cast<const float4*>(src + i));
+    } else {
+        for (int i = lane; i < n; i += 32) dst[i] = from_float<T>(src[i]);
+    }
+}
+
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(32 * ROTARY_WARPS)
 qkv_rotary_store_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ q_norm,
                         const float* __restrict__ k_norm, int norm_mode, float eps, const float* __restrict__ rotations, int rot,
@@ -32,7 +53,7 @@ qkv_rotary_store_kernel(const float* __restrict__ proj, int proj_stride, const f
                         const int* __restrict__ slots, int nq, int nkv, int d, int e, int page_size, int values_from_keys) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float heads[ROTARY_WARPS][ROTARY_MAX_D];
+    __shared__ __align__(16) float heads[ROTARY_WARPS][ROTARY_MAX_D];
     const size_t t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qw = nq * d, kw = nkv * d;
@@ -48,8 +69,7 @@ qkv_rotary_store_kernel(const float* __restrict__ proj, int proj_stride, const f
             if (!store || !v_cache) continue;
             const int head = unit - nq - nkv;
             const float* src = row + qw + kw + head * e;
-            T* dst = v_cache + (((size_t)page * nkv + head) * page_size + in_page) * e;
-            for (int x = lane; x < e; x += 32) dst[x] = from_float<T>(src[x]);
+            copy_out<T, VEC>(v_cache + (((size_t)page * nkv + head) * page_size + in_page) * e, src, e, lane);
             continue;
         }
         const bool is_q = unit < nq;
@@ -57,12 +77,14 @@ qkv_rotary_store_kernel(const float* __restrict__ proj, int proj_stride, const f
         if (!is_q && !store) continue;
         const float* src = row + (is_q ? head * d : qw + head * d);
         float* x = heads[warp];
-        for (int i = lane; i < d; i += 32) x[i] = src[i];
-        if (!is_q && values_from_keys && v_cache) {          // the value is the key as projected
-            T* dst = v_cache + (((size_t)page * nkv + head) * page_size + in_page) * d;
-            for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(src[i]);
+        if (VEC) {
+            for (int i = 4 * lane; i < d; i += 128) *reinterpret_cast<float4*>(x + i) = *reinterpret_cast<const float4*>(src + i);
+        } else {
+            for (int i = lane; i < d; i += 32) x[i] = src[i];
         }
         __syncwarp();
+        if (!is_q && values_from_keys && v_cache)            // the value is the key as projected
+            copy_out<T, VEC>(v_cache + (((size_t)page * nkv + head) * page_size + in_page) * d, x, d, lane);
         const float* w = is_q ? q_norm : k_norm;
         if (norm_mode == 1) head_norm(x, d, w, eps, lane);
         if (turn) {
@@ -76,8 +98,7 @@ qkv_rotary_store_kernel(const float* __restrict__ proj, int proj_stride, const f
             __syncwarp();
         }
         if (norm_mode == 2) head_norm(x, d, w, eps, lane);
-        T* dst = is_q ? q_out + t * qw + (size_t)head * d : k_cache + (((size_t)page * nkv + head) * page_size + in_page) * d;
-        for (int i = lane; i < d; i += 32) dst[i] = from_float<T>(x[i]);
+        copy_out<T, VEC>(is_q ? q_out + t * qw + (size_t)head * d : k_cache + (((size_t)page * nkv + head) * page_size + in_page) * d, x, d, lane);
         __syncwarp();
     }
 }
@@ -94,13 +115,16 @@ MRS_EXPORT int mrs_qkv_rotary_store(int is_bf16, const float* proj, int proj_str
         proj_stride < nq * d + nkv * d + (values_from_keys ? 0 : nkv * e))
         return MRS_BAD_ARGUMENT;
     if (rot == 0) rotations = nullptr;
-    if (is_bf16)
-        MRS_LAUNCH(qkv_rotary_store_kernel<bf16>, tokens, 32 * ROTARY_WARPS, 0, s, proj, proj_stride, q_norm, k_norm, norm_mode, eps,
-                   rotations, rot, interleaved, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, slots, nq, nkv, d, e, page_size,
-                   values_from_keys);
-    else
-        MRS_LAUNCH(qkv_rotary_store_kernel<float>, tokens, 32 * ROTARY_WARPS, 0, s, proj, proj_stride, q_norm, k_norm, norm_mode, eps,
-                   rotations, rot, interleaved, (float*)q_out, (float*)k_cache, (float*)v_cache, slots, nq, nkv, d, e, page_size,
-                   values_from_keys);
+    const bool vec = d % 4 == 0 && e % 4 == 0 && proj_stride % 4 == 0 &&
+                     (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
+#define MRS_ROTARY_STORE(T, VEC)                                                                                                     \
+    MRS_LAUNCH((qkv_rotary_store_kernel<T, VEC>), tokens, 32 * ROTARY_WARPS, 0, s, proj, proj_stride, q_norm, k_norm, norm_mode, eps, \
+               rotations, rot, interleaved, (T*)q_out, (T*)k_cache, (T*)v_cache, slots, nq, nkv, d, e, page_size, values_from_keys)
+    if (is_bf16) {
+        if (vec) MRS_ROTARY_STORE(bf16, true); else MRS_ROTARY_STORE(bf16, false);
+    } else {
+        if (vec) MRS_ROTARY_STORE(float, true); else MRS_ROTARY_STORE(float, false);
+    }
+#undef MRS_ROTARY_STORE
     MRS_RETURN_LAUNCH_STATUS();
 }

@@ -434,7 +434,7 @@ def attention_decode_tma_library(d: int) -> ctypes.CDLL:
         lib.mrs_attention_decode_tma_map.argtypes = [_c_vp, ctypes.c_longlong, _c_int, _c_int, _c_vp]
         lib.mrs_attention_decode_tma_map.restype = _c_int
         lib.mrs_attention_decode_tma.argtypes = [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int,
-                                                 _c_int, _c_float, _c_int, _c_int, _c_vp]
+                                                 _c_int, _c_float, _c_int, _c_int, _c_float, _c_vp]
         lib.mrs_attention_decode_tma.restype = _c_int
         lib.mrs_attention_decode_tma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.mrs_attention_decode_tma_scratch_floats.restype = ctypes.c_longlong
@@ -487,8 +487,9 @@ def kv_tensor_map(cache: torch.Tensor) -> int:
 
 def attention_decode_tma(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int,
                          window: int = 0, splits: int = 1, scale: float | None = None,
-                         scratch: torch.Tensor | None = None) -> None:
-    """Tiles of up to 16 // (nq // nkv) tokens each; keys and values come through bulk tensor copies."""
+                         scratch: torch.Tensor | None = None, cap: float = 0.0) -> None:
+    """Tiles of up to 16 // (nq // nkv) tokens each; keys and values come through bulk tensor copies.  `scale`: of the
+    scores (None: 1 / sqrt(d)); `cap` > 0: the scaled scores are bent into (-cap, cap), cap * tanh(score / cap)."""
     global launch_count
     _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d)
     lib = attention_decode_tma_library(d)
@@ -506,7 +507,7 @@ def attention_decode_tma(q, k_cache, v_cache, positions, block_table, tiles, out
                                         out.data_ptr(), _ptr(scratch) if splits > 1 else None, _ptr(counters), nq, nkv,
                                         k_cache.shape[2],
                                         float(scale if scale is not None else 1.0 / math.sqrt(d)), int(window),
-                                        int(splits), _stream())
+                                        int(splits), float(cap), _stream())
     launch_count += 1
     if code != 0:
         raise BackendError(f"attention_decode_tma: {lib.mrs_attention_decode_tma_error_string(code).decode()} (code {code})")
@@ -541,7 +542,7 @@ def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
         lib.mrs_attention_prefill_tc_kv_map.argtypes = [_c_vp, ctypes.c_longlong, _c_int, _c_int, _c_vp]
         lib.mrs_attention_prefill_tc_q_map.argtypes = [_c_vp, ctypes.c_longlong, _c_int, _c_int, _c_vp]
         lib.mrs_attention_prefill_tc.argtypes = [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_int, _c_int, _c_int, _c_float,
-                                                 _c_int, _c_vp, _c_int, _c_vp]
+                                                 _c_int, _c_vp, _c_int, _c_float, _c_vp]
         lib.mrs_attention_prefill_tc_partial_floats.argtypes = [_c_int, _c_int]
         lib.mrs_attention_prefill_tc_partial_floats.restype = ctypes.c_longlong
         for name in ("mrs_attention_prefill_tc_kv_map", "mrs_attention_prefill_tc_q_map", "mrs_attention_prefill_tc"):
@@ -559,8 +560,9 @@ def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
 
 
 def attention_prefill_tc(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int,
-                         window: int = 0, scale: float | None = None, shares: bool = False) -> None:
-    """Work entries of up to 256 // (nq // nkv) tokens of one request each, on the tcgen05 tensor cores.  The
+                         window: int = 0, scale: float | None = None, shares: bool = False, cap: float = 0.0) -> None:
+    """Work entries of up to 256 // (nq // nkv) tokens of one request each, on the tcgen05 tensor cores; `scale` of the
+    scores (None: 1 / sqrt(d)), `cap` > 0: the scaled scores are bent into (-cap, cap), cap * tanh(score / cap).  The
     fourth number of an entry is 0, or index | count << 8 when `count` entries (one after the other in the list)
     walk one share of the keys each (`shares` says that the list has such entries, whose sums a second kernel
     merges), or gap << 16 when the entry's second tile of 128 // (nq // nkv) tokens starts `gap` tokens behind
@@ -593,7 +595,7 @@ def attention_prefill_tc(q, k_cache, v_cache, positions, block_table, tiles, out
     code = lib.mrs_attention_prefill_tc(q_map, maps[0], maps[1], positions.data_ptr(), block_table.data_ptr(),
                                         block_table.shape[1], tiles.data_ptr(), tiles.shape[0], out.data_ptr(), nq, nkv,
                                         k_cache.shape[2], float(scale if scale is not None else 1.0 / math.sqrt(d)),
-                                        int(window), _ptr(partials), int(shares), _stream())
+                                        int(window), _ptr(partials), int(shares), float(cap), _stream())
     if code != 0:
         fail(code, "attention_prefill_tc")
 

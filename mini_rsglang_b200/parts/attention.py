@@ -237,8 +237,15 @@ def tile_plan_arguments(d: int, group: int, page_size: int, nkv: int, window: in
     return (group, kernels.MMA_ROWS_WIDE, nkv, window, 128, sms)
 
 
-def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) -> None:
-    """Attention of this step's queries over their requests' cached keys and values.  bfloat16
+def fast_kernels_take(d: int, group: int, page_size: int) -> bool:
+    """Whether both tensor-core kernels that are fed by bulk tensor copies take these sizes: the one for few rows and the
+    tcgen05 one for prompt portions (they also take a scale of the scores and a soft cap)."""
+    return kernels.attention_decode_tma_supported(d, group, page_size) and kernels.attention_prefill_tc_supported(d, group, page_size)
+
+
+def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int, scale: float | None = None, cap: float = 0.0) -> None:
+    """Attention of this step's queries over their requests' cached keys and values.  `scale` (None: 1 / sqrt(d)) and a
+    soft cap on the scaled scores (`cap` > 0) are taken only where `fast_kernels_take` the sizes.  bfloat16
     with a head size that is a multiple of 16 runs on the tensor cores: decoded tokens and short
     portions through the kernels for few rows (fed by bulk tensor copies when the head size is a
     multiple of 64), longer portions through the tcgen05 kernel (head sizes 64 and 128) or the
@@ -246,6 +253,8 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
     CUDA-core kernel."""
     table = ctx.block_tables[cache.group]
     group = nq // nkv
+    if (scale is not None or cap) and (q.dtype is not torch.bfloat16 or not fast_kernels_take(d, group, cache.k.shape[2])):
+        raise InvalidRequest("a scale of its own or a soft cap needs the kernels that are fed by bulk tensor copies")
     if q.dtype is not torch.bfloat16 or not kernels.attention_mma_supported(d, group):
         kernels.attention_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, table, out, nq, nkv, d, window)
         return
@@ -257,14 +266,14 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
         if kernels.attention_decode_tma_supported(d, group, cache.k.shape[2]):
             splits = choose_splits(narrow.shape[0], nkv, longest, sms,
                                    clusters=lambda size: kernels.attention_decode_tma_resident_clusters(d, size, q.device))
-            kernels.attention_decode_tma(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
+            kernels.attention_decode_tma(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits, scale=scale, cap=cap)
         else:
             splits = choose_splits(narrow.shape[0], nkv, longest, sms)
             kernels.attention_mma_keys(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
 
     def many_rows():
         if tensor_core_rows:
-            kernels.attention_prefill_tc(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window, shares=shared)
+            kernels.attention_prefill_tc(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window, scale=scale, shares=shared, cap=cap)
         else:
             kernels.attention_mma_rows(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window)
 

@@ -29,7 +29,8 @@ import torch
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .attention import attention_tile_lists, choose_splits, plan_attention_tiles
+from .attention import (attention_tile_lists, choose_splits, fast_kernels_take, paged_attention, plan_attention_tiles,
+                        tile_plan_arguments)
 from .base import MIXERS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, StepFacts
 from .linear import linear
 
@@ -230,7 +231,10 @@ class BiasedWindowAttention(Mixer):
         out = torch.empty((tokens, self.nq * self.e), dtype=dtype, device=device)
         table = ctx.block_tables[cache.group]
         arguments = self._tile_plan()
-        if not arguments:
+        if self._plain_scores():
+            # nothing but scale, cap and window around the scores: the kernels that are fed by bulk tensor copies take them
+            paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window, scale=self.scale, cap=self.softcap)
+        elif not arguments:
             # the 32-bit path and head sizes that the tensor-core kernel does not take: one warp a (token, head)
             kernels.attention_biased_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, table, out, self.nq, self.nkv,
                                           self.d, self.e, self.scale, self.softcap, self.window, self.keep_first,
@@ -251,11 +255,21 @@ class BiasedWindowAttention(Mixer):
             kernels.sigmoid_gate_mul(out, proj[:, proj.shape[1] - self.nq * self.e:])
         return linear(out, self.o, out_dtype=torch.float32)
 
+    def _plain_scores(self) -> bool:
+        """Whether this attention, as it is served, is scale, cap, window and softmax and nothing else (no bias table, no
+        sink, no kept first positions, no chunks, no gate a head, values of the keys' size), at sizes that the kernels fed by
+        bulk tensor copies take."""
+        return (self.runtime.dtype is torch.bfloat16 and self.e == self.d and not self.bias_rows and not self.sink
+                and not self.keep_first and not self.chunk and self.output_gate != "heads"
+                and fast_kernels_take(self.d, self.nq // self.nkv, self.runtime.page_size))
+
     def _tile_plan(self) -> tuple:
         """What the tile planner is asked for this attention ((): no tiles, the CUDA-core kernel takes every row)."""
         if self._plan_arguments is None:
             group = self.nq // self.nkv
-            if self.runtime.dtype is torch.bfloat16 and \
+            if self._plain_scores():
+                self._plan_arguments = tile_plan_arguments(self.d, group, self.runtime.page_size, self.nkv, self.window, self.o.device)
+            elif self.runtime.dtype is torch.bfloat16 and \
                     kernels.attention_biased_mma_supported(self.d, self.e, group, self.runtime.page_size):
                 # the window enters the plan only as the reach of a tile's keys; kept first tokens add a block at most
                 self._plan_arguments = (group, kernels.MMA_ROWS_WIDE, self.nkv, self.window or self.chunk, 128, kernels.sm_count(self.o.device))

@@ -615,6 +615,43 @@ def test_a_window_sees_exactly_its_keys_whose_values_are_the_keys(dtype, window,
                     assert got[h][3].abs() < 1.0, (target, portions, h)
 
 
+@pytest.mark.parametrize("cap", [0.0, 2.0, 30.0])
+@pytest.mark.parametrize("H,G,d,window,page", [(4, 2, 64, 0, 16), (16, 1, 64, 40, 16), (8, 2, 128, 0, 16), (2, 2, 128, 100, 8)])
+def test_scale_and_cap_in_the_kernels_fed_by_bulk_copies(H, G, d, window, page, cap):
+    """The attention of plain scores (scale, cap, window) through the kernel for few rows and the tcgen05 kernel for prompt
+    portions, against the CUDA-core kernel on the same pages: a prompt of 300 tokens in one step, then a portion of 7 and
+    single tokens; scores of a size that the small cap bends hard."""
+    from mini_rsglang_b200 import kernels
+    from mini_rsglang_b200.parts.attention import fast_kernels_take, paged_attention
+
+    assert fast_kernels_take(d, H // G, page)
+    torch.manual_seed(H + d + window)
+    tokens, scale = 320, 2.5 / d ** 0.5
+    pages = -(-tokens // page)
+    order = torch.randperm(pages + 2)[:pages].to(torch.int32)
+    k = torch.randn(pages + 2, G, page, d, device=DEV).bfloat16()
+    v = torch.randn(pages + 2, G, page, d, device=DEV).bfloat16()
+    q_all = (torch.randn(tokens, H * d, device=DEV) * 1.5).bfloat16()
+    cache = types.SimpleNamespace(group=0, k=k, v=v)
+    start = 0
+    for count in (300, 7, 1, 1, 11):
+        ctx = types.SimpleNamespace(shared={}, rehearsal=False, facts=None, plan_views=None, observe=None)
+        ctx.num_tokens, ctx.num_sequences, ctx.real_sequences = count, 1, 1
+        ctx.positions = torch.arange(start, start + count, dtype=torch.int32, device=DEV)
+        ctx.seq_of_token = torch.zeros(count, dtype=torch.int32, device=DEV)
+        ctx.block_tables = [order.view(1, -1).to(DEV)]
+        ctx.host_q_start, ctx.host_start_pos = [0, count], [start]
+        ctx.max_query_len, ctx.max_context_len = count, start + count
+        ctx.decode_tiles = torch.tensor([[0, 0, 1, 0]], dtype=torch.int32, device=DEV) if count == 1 else None
+        q = q_all[start:start + count].contiguous()
+        got, want = torch.empty_like(q), torch.empty_like(q)
+        paged_attention(q, cache, ctx, got, H, G, d, window, scale=scale, cap=cap)
+        kernels.attention_biased_simt(q, k, v, ctx.positions, ctx.seq_of_token, ctx.block_tables[0], want, H, G, d, d, scale, cap, window)
+        kernels.check_device_errors()
+        assert (got.float() - want.float()).abs().max() < 0.03, (count, start)
+        start += count
+
+
 # ----------------------------------------------------------------------------------------------------------------
 # the engine's own entry point and scheduler
 # ----------------------------------------------------------------------------------------------------------------
