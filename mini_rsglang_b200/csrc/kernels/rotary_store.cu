@@ -103,6 +103,87 @@ qkv_rotary_store_kernel(const float* __restrict__ proj, int proj_stride, const f
     }
 }
 
+// The same for heads of up to 128 elements (a multiple of 4) in rows on 16-byte boundaries, with the head in registers: a
+// lane owns four neighbouring elements from the load to the store.  Interleaved pairs lie inside a lane; the partner of a
+// split half lies rot / 8 lanes away (rot a multiple of 8), so a rotation is four shuffles; a norm is one sum over the warp.
+template <typename T>
+__global__ void __launch_bounds__(32 * ROTARY_WARPS)
+qkv_rotary_store_regs_kernel(const float* __restrict__ proj, int proj_stride, const float* __restrict__ q_norm,
+                             const float* __restrict__ k_norm, int norm_mode, float eps, const float* __restrict__ rotations, int rot,
+                             int interleaved, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                             const int* __restrict__ slots, int nq, int nkv, int d, int e, int page_size, int values_from_keys) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qw = nq * d, kw = nkv * d;
+    const float* row = proj + t * proj_stride;
+    const int slot = slots ? slots[t] : -1;
+    const bool store = slot >= 0 && k_cache != nullptr;
+    const int page = store ? slot / page_size : 0, in_page = store ? slot % page_size : 0;
+    const int half = rot / 2;
+    const float* turn = rotations ? rotations + t * (size_t)half * 2 : nullptr;
+    const int units = nq + nkv + (values_from_keys ? 0 : nkv);
+    const int at = 4 * lane;                                  // this lane's first element of a head
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int unit = warp; unit < units; unit += ROTARY_WARPS) {
+        if (unit >= nq + nkv) {                              // a value head with columns of its own
+            if (!store || !v_cache) continue;
+            const int head = unit - nq - nkv;
+            if (at < e) put4<T>(v_cache + (((size_t)page * nkv + head) * page_size + in_page) * e + at,
+                                *reinterpret_cast<const float4*>(row + qw + kw + head * e + at));
+            continue;
+        }
+        const bool is_q = unit < nq;
+        const int head = is_q ? unit : unit - nq;
+        if (!is_q && !store) continue;
+        const bool mine = at < d;
+        float4 x = mine ? *reinterpret_cast<const float4*>(row + (is_q ? head * d : qw + head * d) + at) : zero;
+        if (!is_q && values_from_keys && v_cache && mine)    // the value is the key as projected
+            put4<T>(v_cache + (((size_t)page * nkv + head) * page_size + in_page) * d + at, x);
+        const float* w = is_q ? q_norm : k_norm;
+        const float4 wv = (w && mine && norm_mode) ? *reinterpret_cast<const float4*>(w + at) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if (norm_mode == 1) {
+            const float scale = 1.0f / sqrtf(warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w) / (float)d + eps);
+            x = make_float4(x.x * scale * wv.x, x.y * scale * wv.y, x.z * scale * wv.z, x.w * scale * wv.w);
+        }
+        if (turn) {
+            if (interleaved) {                               // pairs (at, at + 1) and (at + 2, at + 3): pair numbers at / 2 and at / 2 + 1
+                if (at < rot) {
+                    const float2 cs = *reinterpret_cast<const float2*>(turn + at);        // pair at / 2: (cos, sin)
+                    const float u = x.x, v = x.y;
+                    x.x = u * cs.x - v * cs.y, x.y = v * cs.x + u * cs.y;
+                }
+                if (at + 2 < rot) {
+                    const float2 cs = *reinterpret_cast<const float2*>(turn + at + 2);
+                    const float u = x.z, v = x.w;
+                    x.z = u * cs.x - v * cs.y, x.w = v * cs.x + u * cs.y;
+                }
+            } else {
+                const int away = rot / 8;                    // lanes between an element and its partner
+                const bool low = at < half, turns = at < rot;
+                const int partner = turns ? (low ? lane + away : lane - away) : lane;
+                const float4 other = make_float4(__shfl_sync(0xffffffffu, x.x, partner), __shfl_sync(0xffffffffu, x.y, partner),
+                                                 __shfl_sync(0xffffffffu, x.z, partner), __shfl_sync(0xffffffffu, x.w, partner));
+                if (turns) {
+                    // pair i = (i, i + half): the low element becomes u cos - v sin, the high one v cos + u sin
+                    const int i = low ? at : at - half;
+                    const float4 c01 = *reinterpret_cast<const float4*>(turn + 2 * i), c23 = *reinterpret_cast<const float4*>(turn + 2 * i + 4);
+                    const float sign = low ? -1.0f : 1.0f;
+                    x = make_float4(x.x * c01.x + sign * other.x * c01.y, x.y * c01.z + sign * other.y * c01.w,
+                                    x.z * c23.x + sign * other.z * c23.y, x.w * c23.z + sign * other.w * c23.w);
+                }
+            }
+        }
+        if (norm_mode == 2) {
+            const float scale = 1.0f / sqrtf(warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w) / (float)d + eps);
+            x = make_float4(x.x * scale * wv.x, x.y * scale * wv.y, x.z * scale * wv.z, x.w * scale * wv.w);
+        }
+        if (mine)
+            put4<T>(is_q ? q_out + t * qw + (size_t)head * d + at : k_cache + (((size_t)page * nkv + head) * page_size + in_page) * d + at, x);
+    }
+}
+
 }  // namespace
 
 MRS_EXPORT int mrs_qkv_rotary_store(int is_bf16, const float* proj, int proj_stride, const float* q_norm, const float* k_norm,
@@ -117,6 +198,16 @@ MRS_EXPORT int mrs_qkv_rotary_store(int is_bf16, const float* proj, int proj_str
     if (rot == 0) rotations = nullptr;
     const bool vec = d % 4 == 0 && e % 4 == 0 && proj_stride % 4 == 0 &&
                      (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0;
+    // heads that fit a warp's registers, four elements a lane: split halves need the partner a whole number of lanes away
+    if (vec && d <= 128 && e <= 128 && (rot == 0 || (interleaved ? rot % 2 == 0 : rot % 8 == 0)) && (((uintptr_t)q_norm | (uintptr_t)k_norm) & 15) == 0) {
+        if (is_bf16)
+            MRS_LAUNCH(qkv_rotary_store_regs_kernel<bf16>, tokens, 32 * ROTARY_WARPS, 0, s, proj, proj_stride, q_norm, k_norm, norm_mode, eps,
+                       rotations, rot, interleaved, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, slots, nq, nkv, d, e, page_size, values_from_keys);
+        else
+            MRS_LAUNCH(qkv_rotary_store_regs_kernel<float>, tokens, 32 * ROTARY_WARPS, 0, s, proj, proj_stride, q_norm, k_norm, norm_mode, eps,
+                       rotations, rot, interleaved, (float*)q_out, (float*)k_cache, (float*)v_cache, slots, nq, nkv, d, e, page_size, values_from_keys);
+        MRS_RETURN_LAUNCH_STATUS();
+    }
 #define MRS_ROTARY_STORE(T, VEC)                                                                                                     \
     MRS_LAUNCH((qkv_rotary_store_kernel<T, VEC>), tokens, 32 * ROTARY_WARPS, 0, s, proj, proj_stride, q_norm, k_norm, norm_mode, eps, \
                rotations, rot, interleaved, (T*)q_out, (T*)k_cache, (T*)v_cache, slots, nq, nkv, d, e, page_size, values_from_keys)

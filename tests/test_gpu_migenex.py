@@ -267,7 +267,8 @@ def rotation_table(positions, dims, base):
 @pytest.mark.parametrize("place,weights", [("before_rotation", True), ("after_rotation", False), ("after_rotation", True), (None, False)])
 @pytest.mark.parametrize("pairing", ["split_half", "interleaved"])
 @pytest.mark.parametrize("H,G,d,e,dims,page,from_keys", [(6, 2, 24, 20, 12, 4, False), (2, 2, 8, 8, 8, 8, True), (16, 2, 64, 64, 32, 16, True),
-                                                         (1, 1, 130, 16, 130, 4, False), (3, 1, 48, 48, 0, 16, True), (5, 5, 256, 256, 2, 16, False)])
+                                                         (1, 1, 130, 16, 130, 4, False), (3, 1, 48, 48, 0, 16, True), (5, 5, 256, 256, 2, 16, False),
+                                                         (2, 1, 16, 16, 6, 4, True), (4, 2, 128, 128, 128, 16, True), (2, 2, 128, 64, 64, 8, False)])
 def test_rotated_and_normed_heads_on_the_way_into_the_cache(H, G, d, e, dims, page, from_keys, pairing, place, weights, far):
     """The kernel after the fused projection: rotation of all, a part or none of a head in either pairing, at positions up
     to thousands; the head norm before or after it, with or without weights; keys at scattered slots; values from columns
