@@ -93,9 +93,18 @@ SHAPE_Z = {"architecture": "Migenex", "vocab": 131, "width": 96, "norm": {"eps":
     dict(keyed(2, 1, 80, 80, 5, base=50.0), mlp=moe(6, 2, 24))]}
 SHAPE_W = dict(copy.deepcopy(SHAPE_Z), loop={"start": 1, "stop": 3, "times": 2}, residual_mult=0.7,
                embedding={"scale": 0.5, "bigram": {"buckets": 300, "mul_prev": 1000003, "mul_cur": 31}})
-SHAPES = {"X": (SHAPE_X, 4), "Y": (SHAPE_Y, 16), "Z": (SHAPE_Z, 16), "W": (SHAPE_W, 8)}
+# V: heads of 64 and 128 whose attentions take the kernels fed by bulk tensor copies (in bfloat16): windows of 24 and 70
+# positions whose passed pages go back to the pool while a request runs, a capped attention over everything, two passes
+# over all three layers.
+SHAPE_V = {"architecture": "Migenex", "vocab": 151, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.6,
+           "embedding": {"scale": 1.5, "bigram": {"buckets": 77, "mul_prev": 13, "mul_cur": 5}},
+           "loop": {"start": 0, "stop": 3, "times": 2}, "layers": [
+               dict(keyed(4, 2, 64, 64, 24), mlp=dense(192)),
+               dict(full(4, 1, 128, 128, 128, cap=5.0), mlp=moe(4, 2, 32, shared=64)),
+               dict(keyed(2, 1, 128, 64, 70, base=300.0), mlp=None)]}
+SHAPES = {"X": (SHAPE_X, 4), "Y": (SHAPE_Y, 16), "Z": (SHAPE_Z, 16), "W": (SHAPE_W, 8), "V": (SHAPE_V, 16)}
 LENGTHS = {"X": [70, 45, 33, 100, 130, 64, 37, 90], "Y": [1, 7, 17, 40, 129, 65, 96, 50], "Z": [40, 75, 23, 58, 66, 31],
-           "W": [50, 2, 81, 64, 33, 47]}
+           "W": [50, 2, 81, 64, 33, 47], "V": [150, 40, 97, 200, 64, 130]}
 MODES = ("whole", "decode_tail", "portions", "mixed")
 
 
@@ -204,7 +213,7 @@ def replay(folders, name, dtype, tmp_path_factory):
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["X", "Y", "Z", "W"])
+@pytest.mark.parametrize("name", ["X", "Y", "Z", "W", "V"])
 def test_replay_matches_plain(folders, tmp_path_factory, name, dtype, mode):
     """Prefill against token-by-token decoding (the tail of 40 tokens lets the windows of 1, 5, 7, 16, 19 and 33 pass over
     decoded tokens), portions of every size (the token before a portion comes from the request's state), batches against
