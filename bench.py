@@ -292,7 +292,7 @@ def looped_configs(size: dict, vocab: int = 32768):
                         "rot": rot}}
     runs = size["layers"]
     layers = [keyed if i % 2 == 0 else routed for i in range(runs - 2)]
-    migenex = {"architecture": "Migenex", "vocab": vocab, "width": w, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+    migenex = {"architecture": "Migenex", "vocab": vocab, "width": w, "norm": {"eps": 1e-6}, "residual_mult": 0.8,
                "embedding": {"scale": 1.0, "bigram": {"buckets": 65536, "mul_prev": 1000003, "mul_cur": 31}},
                "loop": {"start": 2, "stop": 4, "times": 2}, "layers": layers}
     return migenex, latent_configs(size, vocab)[0]

@@ -323,11 +323,11 @@ __global__ void moe_gather_scaled_rows_kernel(const T* __restrict__ x, const int
     for (int i = threadIdx.x; i < k; i += blockDim.x) dst[i] = from_float<T>(pair >= 0 ? to_float(src[i]) * w : 0.0f);
 }
 
-// One block a token.
-template <typename T>
+// One block a token.  O: the sums leave as T, or as float32 (for a float32 norm or residual sum that reads them).
+template <typename T, typename O>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict__ h, const T* __restrict__ shared_out,
                                    const int* __restrict__ chosen, const float* __restrict__ weights, const float* __restrict__ shared_gate,
-                                   T* __restrict__ out, int width, int top, int routed) {
+                                   O* __restrict__ out, int width, int top, int routed) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -340,7 +340,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const T* __restrict_
             v += (weights ? weights[pair] : 1.0f) * part;                                  // no weights: they were applied before
         }
         if (shared_out) v += gate * to_float(shared_out[(size_t)t * width + i]);
-        out[(size_t)t * width + i] = from_float<T>(v);
+        out[(size_t)t * width + i] = from_float<O>(v);
     }
 }
 
@@ -383,10 +383,10 @@ __global__ void moe_gather_scaled_rows_vec_kernel(const T* __restrict__ x, const
     }
 }
 
-template <typename T>
+template <typename T, typename O>
 __global__ void moe_combine_vec_kernel(const T* __restrict__ y, const T* __restrict__ h, const T* __restrict__ shared_out,
                                        const int* __restrict__ chosen, const float* __restrict__ weights, const float* __restrict__ shared_gate,
-                                       T* __restrict__ out, int width, int top, int routed) {
+                                       O* __restrict__ out, int width, int top, int routed) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int V = Piece<T>::N;
@@ -416,7 +416,13 @@ __global__ void moe_combine_vec_kernel(const T* __restrict__ y, const T* __restr
 #pragma unroll
             for (int e = 0; e < V; ++e) v[e] += gate * part[e];
         }
-        Store16<T>::store(out + (size_t)t * width + i, v);
+        if (sizeof(O) == sizeof(T)) {
+            Store16<T>::store(reinterpret_cast<T*>(out) + (size_t)t * width + i, v);
+        } else {                                   // float32 sums of bfloat16 parts: eight floats, two stores
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)t * width + i);
+#pragma unroll
+            for (int e = 0; e < V / 4; ++e) dst[e] = make_float4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
+        }
     }
 }
 
@@ -525,25 +531,24 @@ MRS_EXPORT int mrs_moe_gather_scaled_rows(int is_bf16, const void* x, const int*
 }
 
 MRS_EXPORT int mrs_moe_combine(int is_bf16, const void* y, const void* h, const void* shared_out, const int* chosen, const float* weights,
-                               const float* shared_gate, void* out, int tokens, int width, int top, int routed, void* stream) {
+                               const float* shared_gate, void* out, int tokens, int width, int top, int routed, int out_float32, void* stream) {
     if (tokens <= 0) return 0;
     if (width <= 0 || top <= 0) return MRS_BAD_ARGUMENT;
     const int threads = width >= 1024 ? 256 : 128;
     const bool aligned = (((uintptr_t)y | (uintptr_t)h | (uintptr_t)shared_out | (uintptr_t)out) & 15) == 0;
-    if (aligned && width % (is_bf16 ? 8 : 4) == 0) {
-        if (is_bf16)
-            MRS_LAUNCH(moe_combine_vec_kernel<bf16>, tokens, 128, 0, stream, (const bf16*)y, (const bf16*)h, (const bf16*)shared_out, chosen,
-                       weights, shared_gate, (bf16*)out, width, top, routed);
-        else
-            MRS_LAUNCH(moe_combine_vec_kernel<float>, tokens, 128, 0, stream, (const float*)y, (const float*)h, (const float*)shared_out,
-                       chosen, weights, shared_gate, (float*)out, width, top, routed);
-        MRS_RETURN_LAUNCH_STATUS();
-    }
-    if (is_bf16)
-        MRS_LAUNCH(moe_combine_kernel<bf16>, tokens, threads, 0, stream, (const bf16*)y, (const bf16*)h, (const bf16*)shared_out, chosen,
-                   weights, shared_gate, (bf16*)out, width, top, routed);
-    else
-        MRS_LAUNCH(moe_combine_kernel<float>, tokens, threads, 0, stream, (const float*)y, (const float*)h, (const float*)shared_out,
-                   chosen, weights, shared_gate, (float*)out, width, top, routed);
+    const bool vec = aligned && width % (is_bf16 ? 8 : 4) == 0;
+#define MRS_MOE_COMBINE(T, O)                                                                                                          \
+    do {                                                                                                                               \
+        if (vec)                                                                                                                       \
+            MRS_LAUNCH((moe_combine_vec_kernel<T, O>), tokens, 128, 0, stream, (const T*)y, (const T*)h, (const T*)shared_out, chosen,   \
+                       weights, shared_gate, (O*)out, width, top, routed);                                                             \
+        else                                                                                                                           \
+            MRS_LAUNCH((moe_combine_kernel<T, O>), tokens, threads, 0, stream, (const T*)y, (const T*)h, (const T*)shared_out, chosen,   \
+                       weights, shared_gate, (O*)out, width, top, routed);                                                             \
+    } while (0)
+    if (!is_bf16) MRS_MOE_COMBINE(float, float);
+    else if (out_float32) MRS_MOE_COMBINE(bf16, float);
+    else MRS_MOE_COMBINE(bf16, bf16);
+#undef MRS_MOE_COMBINE
     MRS_RETURN_LAUNCH_STATUS();
 }

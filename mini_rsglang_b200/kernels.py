@@ -1443,7 +1443,7 @@ _EXPERT_SIGNATURES = {
     "mrs_moe_gather_rows": [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_moe_gather_scaled_rows": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_moe_product_mma": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
-    "mrs_moe_combine": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_moe_combine": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
 }
 _latent_lib = None
 _expert_lib = None
@@ -1854,7 +1854,7 @@ def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tenso
                 weights: torch.Tensor | None, shared_gate: torch.Tensor | None, out: torch.Tensor, routed: int) -> None:
     """out[token] = sum over its choices of weight * (y[pair] for one of the first `routed` experts, else h[token])
     (+ shared_gate[token] * shared_out[token]).  `weights` None: every weight is 1 (they were applied to the experts' inputs);
-    `shared_gate` None: the shared expert's output counts fully."""
+    `shared_gate` None: the shared expert's output counts fully.  `out` has h's dtype, or float32 (the sums as they are)."""
     tokens, width = h.shape
     top = chosen.shape[1]
     _need(h, None, "expert input", (tokens, width))
@@ -1862,7 +1862,9 @@ def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tenso
         _need(y, h.dtype, "expert outputs", (tokens * top, width))
     elif routed > 0:
         raise InvalidRequest("moe_combine: experts with weights need their outputs")
-    _need(out, h.dtype, "combined output", (tokens, width))
+    if out.dtype is not torch.float32:
+        _need(out, h.dtype, "combined output", (tokens, width))
+    _need(out, None, "combined output", (tokens, width))
     _need(chosen, torch.int32, "chosen experts", (tokens, top))
     if weights is not None:
         _need(weights, torch.float32, "expert weights", (tokens, top))
@@ -1871,7 +1873,8 @@ def moe_combine(y: torch.Tensor | None, h: torch.Tensor, shared_out: torch.Tenso
         if shared_gate is not None:
             _need(shared_gate, torch.float32, "shared gate", (tokens,))
     _check(expert_library().mrs_moe_combine(_is_bf16(h.dtype), _ptr(y), h.data_ptr(), _ptr(shared_out), chosen.data_ptr(), _ptr(weights),
-                                            _ptr(shared_gate), out.data_ptr(), tokens, width, top, routed, _stream()), "moe_combine")
+                                            _ptr(shared_gate), out.data_ptr(), tokens, width, top, routed,
+                                            int(out.dtype is torch.float32), _stream()), "moe_combine")
 
 
 # ------------------------------------------------------------------------------------------------

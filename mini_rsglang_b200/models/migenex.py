@@ -67,7 +67,7 @@ def migenex_spec(config: MigenexConfig) -> ModelSpec:
                 feed_forward = PartSpec("routed_experts", {
                     "width": c.width, "experts": mlp["router"]["experts"], "top": mlp["router"]["top"], "inner": mlp["expert"]["ff"],
                     "score": "sigmoid", "normalize": False, "form": "plain", "activation": EXPERT_ACTIVATION, "weight_on": "input",
-                    "shared": shared, "names": EXPERT_NAMES})
+                    "float32_out": True, "shared": shared, "names": EXPERT_NAMES})
             parts.update(norm2=norm, norm2b=norm, feed_forward=feed_forward)
             names.update(norm2="norm2", norm2b="norm2b", feed_forward="mlp")
         layers.append(LayerSpec(f"l{i}", "sandwich_norm", parts, names, {"branch_scale": c.residual_mult}))

@@ -33,7 +33,7 @@ class RoutedExperts(FeedForward):
     def __init__(self, prefix: str, width: int, experts: int, top: int, inner: int, identity: int = 0, scale: float = 1.0,
                  score: str = "softmax", correction: bool = False, shared: PartSpec | None = None, shared_gate: bool = False,
                  normalize: bool = True, form: str = "gated", activation: str = "silu", weight_on: str = "output",
-                 names: dict | None = None):
+                 float32_out: bool = False, names: dict | None = None):
         """`experts` with tensors, then `identity` without; `shared`: the feed-forward that every token passes as well
         (its root is the leaf "shared" below this part's), `shared_gate`: behind a sigmoid gate of one number a token.
         `names`: leaves below the part's root; "expert" is a pattern with `{}` for the expert's number."""
@@ -48,6 +48,7 @@ class RoutedExperts(FeedForward):
             raise InvalidRequest(f"{prefix}: router scores {score!r} are not built; softmax or sigmoid")
         self.score, self.correction = score, bool(correction)
         self.normalize, self.form, self.activation, self.weight_on = bool(normalize), form, activation, weight_on
+        self.float32_out = bool(float32_out)       # the summed outputs leave as float32 (a float32 norm or sum reads them)
         if form not in ("gated", "plain") or weight_on not in ("output", "input"):
             raise InvalidRequest(f"{prefix}: experts are 'gated' or 'plain', their weights on the 'output' or the 'input'")
         if form == "gated" and activation != "silu":
@@ -139,6 +140,6 @@ class RoutedExperts(FeedForward):
             else:
                 kernels.moe_experts(h, chosen, self.gate_up, self.down, y, self.experts, block=self.block)
         shared_out = self.shared.forward(h, ctx) if self.shared is not None else None       # no gate: it counts fully
-        out = torch.empty((tokens, self.width), dtype=dtype, device=device)
+        out = torch.empty((tokens, self.width), dtype=torch.float32 if self.float32_out else dtype, device=device)
         kernels.moe_combine(y, h, shared_out, chosen, None if on_input else weights, shared_gate, out, self.experts)
         return out
