@@ -177,7 +177,7 @@ BF16_NRMSE = 0.03
 
 
 def check_rows(got, want, dtype, what, tally=None):
-    """`tally`: a list that collects the rows' errors (the caller then judges them together with `judge`)."""
+    """`tally`: a list that collects the rows' errors (the caller then weighs them together with `settle`)."""
     if dtype == "float32":
         return T.check_rows(got, want, dtype, what)
     assert got.shape == want.shape and torch.isfinite(got).all(), what
@@ -188,10 +188,10 @@ def check_rows(got, want, dtype, what, tally=None):
         assert nrmse <= 1.5 * BF16_NRMSE and cosine >= T.BF16_COSINE, f"{what} row {i}: NRMSE {nrmse:.4f}, cosine {cosine:.5f}"
         own.append((nrmse, f"{what} row {i}"))
     if tally is None:
-        judge(own)
+        settle(own)
 
 
-def judge(tally):
+def settle(tally):
     over = [entry for entry in tally if entry[0] > BF16_NRMSE]
     assert len(over) <= max(1, len(tally) // 50), f"{len(over)} of {len(tally)} rows beyond {BF16_NRMSE}: {over[:5]}"
 
@@ -236,7 +236,7 @@ def test_replay_matches_plain(folders, tmp_path_factory, name, dtype, mode):
     tally = []
     for step, got, want, _ in rows:
         check_rows(got, want, dtype, f"{name} {dtype} {mode} step {step}", tally)
-    judge(tally)
+    settle(tally)
 
 
 @pytest.mark.parametrize("name", ["X", "Y"])
